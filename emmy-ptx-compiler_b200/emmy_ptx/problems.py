@@ -367,9 +367,3 @@ WORKLOADS = {"sum": array_sum, "softmax": row_softmax, "matmul": matmul_f16, "at
 def write_all(root) -> list:
     """The five full-size workloads."""
     return [write(make(), root) for make in WORKLOADS.values()]
-
-
-if __name__ == "__main__":
-    import sys
-    for p in write_all(sys.argv[1] if len(sys.argv) > 1 else Path(__file__).resolve().parent.parent / "problems"):
-        print(p)

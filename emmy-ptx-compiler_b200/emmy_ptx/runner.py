@@ -1,0 +1,218 @@
+"""The local runner: what the reference's remote service did, on this machine's GPU.
+
+The reference posts PTX to an HTTP service that assembles it (``/compile``) and
+launches it (``/run``) with inputs made from the ``seed`` of each argument in
+``meta.json`` (tools/run_suite.py:66-111; inputs are
+``np.random.default_rng(seed).standard_normal(shape).astype(dtype)``, checked
+against the shipped ``expected.npz`` files). ``Problem`` does the same locally:
+compile every kernel of the folder (compile.py's ``compile_file``), assemble
+with ptxas, load through libemmyb200.so, allocate torch tensors for the
+arguments, chain ``intermediate`` arguments from the kernel that produced them
+(:81-85), zero the ``zero_outputs``, launch in order, and time with CUDA events
+(median of 20 after 3 warm-ups is the reference's protocol, :91).
+
+Additions to ``meta.json`` arguments understood here (all optional): ``dist``
+("normal" default, "uniform_pm1"), ``scale`` (multiplies the draw), ``quant``
+(per-tensor e4m3 quantisation; names the argument that receives the scale) and
+``scale_of``. The launch itself comes from the module's ``// launch:`` header
+when it has one (a template may need its own geometry, a cluster size, dynamic
+shared memory or tensor maps), else from ``meta.json`` as in the reference.
+"""
+
+from __future__ import annotations
+
+import json
+import re
+from pathlib import Path
+
+import numpy as np
+
+from . import compile_file, driver, toolchain
+
+TORCH_DTYPE = {"f32": "float32", "f64": "float64", "f16": "float16", "bf16": "bfloat16", "i32": "int32", "i64": "int64",
+               "u8": "uint8", "i8": "int8", "i16": "int16", "bool": "uint8", "f8e4m3": "uint8", "f8e5m2": "uint8"}
+NUMPY_DTYPE = {"f32": np.float32, "f64": np.float64, "f16": np.float16, "i32": np.int32, "i64": np.int64, "u8": np.uint8,
+               "i8": np.int8, "i16": np.int16, "u32": np.uint32, "bool": np.uint8}
+
+
+def numpy_dtype(name: str):
+    if name == "bf16":
+        import ml_dtypes
+        return ml_dtypes.bfloat16
+    if name in ("f8e4m3", "f8e5m2"):
+        return np.uint8
+    return NUMPY_DTYPE[name]
+
+
+def quantize_e4m3(w: np.ndarray) -> tuple:
+    """Per-tensor e4m3 codes and f32 scale: s = max|w| / 448, code = e4m3(w / s), round to nearest
+    even, saturating at +-448 (the encode of emmy_ptx/elementwise.py:113-123; ml_dtypes would give
+    NaN past 464, so the quotient is clamped first)."""
+    import ml_dtypes
+    s = np.float32(np.max(np.abs(w)) / 448.0)
+    q = np.clip(w.astype(np.float32) / s, -448.0, 448.0)
+    return q.astype(ml_dtypes.float8_e4m3fn).view(np.uint8), s
+
+
+def host_inputs(args: list) -> dict:
+    """name -> numpy array for every argument that is neither an output nor an intermediate."""
+    out, scales = {}, {}
+    for a in args:
+        if a.get("output") or a.get("intermediate") or "scale_of" in a:
+            continue
+        if "data" in a:
+            out[a["name"]] = np.array(a["data"], numpy_dtype(a["dtype"])).reshape(a["shape"])
+            continue
+        rng = np.random.default_rng(a.get("seed", 0))
+        if a.get("dist", "normal") == "uniform_pm1":
+            draw = rng.uniform(-1.0, 1.0, a["shape"])
+        else:
+            draw = rng.standard_normal(a["shape"])
+        if "scale" in a:
+            draw = draw * a["scale"]
+        if "quant" in a:
+            codes, s = quantize_e4m3(draw.astype(np.float32))
+            out[a["name"]] = codes
+            scales[a["name"]] = s
+        else:
+            out[a["name"]] = draw.astype(numpy_dtype(a["dtype"]))
+    for a in args:
+        if "scale_of" in a:
+            out[a["name"]] = np.array([scales[a["scale_of"]]], np.float32)
+    return out
+
+
+def to_torch(array: np.ndarray, dtype: str, device):
+    import torch
+    if dtype == "bf16":
+        return torch.from_numpy(array.view(np.int16).copy()).view(torch.bfloat16).to(device)
+    return torch.from_numpy(np.ascontiguousarray(array)).to(device)
+
+
+def to_numpy(tensor, dtype: str) -> np.ndarray:
+    import torch
+    t = tensor.detach().cpu()
+    if dtype == "bf16":
+        import ml_dtypes
+        return t.view(torch.int16).numpy().view(ml_dtypes.bfloat16)
+    return t.numpy()
+
+
+def parse_launch(ptx: str):
+    m = re.search(r"^// launch: (\{.*\})$", ptx, re.M)
+    return json.loads(m.group(1)) if m else None
+
+
+class CompiledKernel:
+    """One kernel of a problem: PTX, cubin, ptxas resources, loaded function."""
+
+    def __init__(self, ir_path: Path, meta: dict, mode: dict):
+        self.meta, self.ir_path = meta, ir_path
+        self.ptx = compile_file(str(ir_path), **mode)
+        self.launch_info = parse_launch(self.ptx) or dict(
+            grid=meta["grid"], block=meta["block"], cluster=1, smem_bytes=meta.get("smem_bytes", 0),
+            params=[dict(kind="buffer", name=n) for n in meta["arg_order"]], family="foreign")
+        cubin, info = toolchain.assemble(self.ptx)
+        self.resources = info.get(meta["entry"], {})
+        self.module = driver.Module(cubin)
+        self.function = self.module.function(meta["entry"])
+
+    def bind(self, tensors: dict) -> driver.Launch:
+        li = self.launch_info
+        params = []
+        for p in li["params"]:
+            if p["kind"] == "buffer":
+                params.append(tensors[p["name"]].data_ptr())
+            elif p["kind"] == "tmap":
+                t = tensors[p["buffer"]]
+                params.append(driver.TensorMap(t.data_ptr() + p.get("offset_bytes", 0), p["dtype"], p["dims"], p["strides_bytes"],
+                                               p["box"], p.get("swizzle", "128B")))
+            else:
+                raise ValueError(f"unknown parameter kind {p['kind']!r}")
+        return driver.Launch(self.function, li["grid"], li["block"], li.get("cluster", 1), li.get("smem_bytes", 0), params)
+
+
+class Problem:
+    """A problem folder compiled in one mode and bound to tensors on one device."""
+
+    def __init__(self, folder, mode: str = "optimized", device: int = 0, inputs: dict | None = None, scratch: dict | None = None):
+        import torch
+        self.folder = Path(folder)
+        self.meta = json.loads((self.folder / "meta.json").read_text())
+        self.mode = mode
+        flags = {"optimized": {}, "strict": {"strict": True}, "plain": {"plain": True}}[mode]
+        if not torch.cuda.is_available():
+            raise driver.EmbError(-101, "no CUDA device: the kernels run on the GPU only")
+        self.device = torch.device("cuda", device)
+        torch.cuda.set_device(self.device)
+        driver.init(device)
+        self.kernels = [CompiledKernel(self.folder / f"{k['entry']}.ir.json", k, flags) for k in self.meta["kernels"]]
+        self.tensors: dict = {}
+        self.dtypes: dict = {}
+        self.host: dict = {}
+        for k in self.meta["kernels"]:
+            given = inputs if inputs is not None else host_inputs(k["args"])
+            for a in k["args"]:
+                name = a["name"]
+                self.dtypes.setdefault(name, a["dtype"])
+                if name in self.tensors:
+                    continue
+                if a.get("output") or a.get("intermediate"):
+                    shape = a["shape"] or [1]
+                    self.tensors[name] = torch.zeros(shape, dtype=getattr(torch, TORCH_DTYPE[a["dtype"]]), device=self.device)
+                else:
+                    self.host[name] = given[name]
+                    self.tensors[name] = to_torch(given[name], a["dtype"], self.device)
+        self.launches = [k.bind(self.tensors) for k in self.kernels]
+        self.zero = [n for k in self.meta["kernels"] for n in k.get("zero_outputs", ())]
+
+    @property
+    def stream(self) -> int:
+        import torch
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def run(self) -> dict:
+        """Launch the chain once and return the final kernels' outputs as numpy arrays."""
+        import torch
+        for n in self.zero:
+            self.tensors[n].zero_()
+        driver.launch(self.launches, self.stream)
+        torch.cuda.synchronize(self.device)
+        return self.outputs()
+
+    def outputs(self) -> dict:
+        names = [a["name"] for k in self.meta["kernels"] for a in k["args"] if a.get("output")]
+        return {n: to_numpy(self.tensors[n], self.dtypes[n]) for n in names}
+
+    def time_us(self, warmup: int = 3, iters: int = 20, flush=None) -> list:
+        return driver.time_chain(self.launches, self.stream, warmup, iters, flush)
+
+    def launch_count(self) -> int:
+        return len(self.launches)
+
+
+def run_source(src, arrays: dict, mode: str = "optimized", device: int = 0) -> dict:
+    """Lower a ``KernelSource`` built in memory (as the reference's tests do,
+    tests/test_gpu_lowering.py:63-80), run it once on ``arrays`` (name -> numpy array, outputs
+    included) and return every buffer the kernel writes."""
+    import torch
+
+    from . import PTX_VERSION, TARGET
+    from .lower import Lowerer
+    flags = {"optimized": {}, "strict": {"strict": True}, "plain": {"plain": True}}[mode]
+    kernel = Lowerer(src, **flags).run()
+    ptx = kernel.render(PTX_VERSION, TARGET)
+    cubin, _ = toolchain.assemble(ptx)
+    if not torch.cuda.is_available():
+        raise driver.EmbError(-101, "no CUDA device: the kernels run on the GPU only")
+    dev = torch.device("cuda", device)
+    torch.cuda.set_device(dev)
+    driver.init(device)
+    fn = driver.Module(cubin).function(src.name)
+    tensors = {n: to_torch(a, src.buffers[n].dtype, dev) for n, a in arrays.items()}
+    li = kernel.launch
+    params = [tensors[p["name"]].data_ptr() for p in li["params"]]
+    launch = driver.Launch(fn, li["grid"], li["block"], li["cluster"], li["smem_bytes"], params)
+    driver.launch([launch], torch.cuda.current_stream(dev).cuda_stream)
+    torch.cuda.synchronize(dev)
+    return {n: to_numpy(tensors[n], src.buffers[n].dtype) for n in src.written}

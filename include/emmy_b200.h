@@ -1,0 +1,116 @@
+/*
+ * emmy_b200.h - C ABI of libemmyb200.so, the launch side of the B200 backend.
+ *
+ * What it replaces. The reference compiler writes PTX text to stdout and stops
+ * there; assembling and launching happen in a remote HTTP service that is not
+ * part of it (tools/run_suite.py:77-92: POST /compile {ptx} -> cubin id and
+ * register counts; POST /run {entry, grid, block, smem_bytes, zero_outputs,
+ * args, warmup, iters} -> median_us and outputs; the same two calls in
+ * tests/test_gpu_lowering.py:70-80 and tests/test_oracle.py:236-253). This
+ * library is the local stand-in for that service: it loads a module image
+ * (PTX text or a cubin made by ptxas), resolves an entry point, launches it on
+ * caller-owned device buffers with the geometry of meta.json, and times it
+ * with CUDA events. It is a thin layer over the CUDA driver API
+ * (cuModuleLoadData, cuLaunchKernelEx, cuTensorMapEncodeTiled).
+ *
+ * Conventions. Plain C types only. Every function returns 0 on success, a
+ * CUresult value (> 0) when the driver refused, or a negative EMB_E_* code;
+ * emb_last_error() then gives a text for the calling thread. The caller owns
+ * all device memory (the Python host passes torch tensors' data pointers);
+ * the library owns the modules it loaded until emb_module_unload. The library
+ * uses the device's primary context, the one the CUDA runtime and torch use,
+ * so pointers and streams are interchangeable. Calls are thread-safe as far
+ * as the driver's are; there is no global state beyond the context.
+ */
+#ifndef EMMY_B200_H
+#define EMMY_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EMB_E_NO_DRIVER (-1)  /* libcuda could not be loaded (no GPU driver on this machine) */
+#define EMB_E_ARGUMENT (-2)   /* an argument is out of range; see emb_last_error() */
+#define EMB_E_DEVICE_STATUS (-3) /* a kernel reported a bounded wait that ran out (status word non-zero) */
+
+/* Element types of a tensor map (values of CUtensorMapDataType are not exposed). */
+enum { EMB_U8 = 0, EMB_F16 = 1, EMB_BF16 = 2, EMB_F32 = 3, EMB_U16 = 4, EMB_U32 = 5 };
+/* Shared-memory swizzle of a tensor-map box. */
+enum { EMB_SWIZZLE_NONE = 0, EMB_SWIZZLE_32B = 1, EMB_SWIZZLE_64B = 2, EMB_SWIZZLE_128B = 3 };
+
+/* One kernel launch: what the runner's POST /run carries per kernel
+ * (tools/run_suite.py:86-92: entry, grid, block, smem_bytes, args), with
+ * `cluster_x` for modules that ask for thread-block clusters
+ * (emmy_ptx/ptx.py:294-295 .reqnctapercluster). `params[i]` points at the
+ * i-th kernel parameter's value: an 8-byte device pointer for a buffer
+ * (the reference's only parameter kind, `.param .u64 p_<buffer>`,
+ * emmy_ptx/ptx.py:288), or a 128-byte tensor map made by emb_tensor_map. */
+typedef struct emb_launch_t {
+    void* fn;
+    uint32_t grid[3];
+    uint32_t block[3];
+    uint32_t cluster_x;  /* 0 or 1: no cluster attribute */
+    uint32_t smem_bytes; /* dynamic shared memory */
+    void** params;
+    int32_t nparams;
+} emb_launch_t;
+
+/* Bind the calling thread to `device`'s primary context (retained once per
+ * device). Must be called before the other functions; cheap to repeat. */
+int emb_init(int device);
+
+/* POST /compile's job after ptxas (tools/run_suite.py:77-80): make a module
+ * from PTX text (NUL-terminated, JIT-compiled by the driver) or from a cubin
+ * image. `nbytes` is the image size (for the record; the driver reads the
+ * image's own length). */
+int emb_module_load(const void* image, size_t nbytes, void** module_out);
+int emb_module_unload(void* module);
+
+/* The entry point named by meta.json's `entry` (tools/run_suite.py:88). */
+int emb_get_function(void* module, const char* entry, void** fn_out);
+
+/* Registers per thread, static shared bytes, local (spill) bytes per thread,
+ * max threads per block: the `registers` figure POST /compile returns
+ * (tools/run_suite.py:80,93) and its companions. Any out pointer may be NULL. */
+int emb_function_info(void* fn, int* registers, int* static_smem, int* local_bytes, int* max_threads);
+
+/* Launch one kernel / a chain of kernels in order on `stream` (a CUstream /
+ * cudaStream_t; NULL is the legacy default stream). Raises the function's
+ * dynamic shared memory limit when smem_bytes needs it. Asynchronous. */
+int emb_launch(const emb_launch_t* launch, void* stream);
+int emb_launch_chain(const emb_launch_t* launches, int n, void* stream);
+
+/* POST /run's timing (tools/run_suite.py:91: warm-ups, then `iters` timed
+ * launches; the reference reports their median): run the chain `warmup` times,
+ * then `iters` times with a CUDA event pair around each run of the chain on
+ * `stream`, and write the `iters` durations in microseconds to `us_out`.
+ * If `flush_ptr` is non-NULL, `flush_bytes` of it are overwritten before every
+ * timed run (outside the event pair) to evict the L2 cache. Synchronous. */
+int emb_time_chain(const emb_launch_t* launches, int n, void* stream, int warmup, int iters,
+                   void* flush_ptr, size_t flush_bytes, float* us_out);
+
+/* Build a tiled TMA descriptor (CUtensorMap, 128 bytes, 64-byte aligned
+ * storage supplied by the caller) over a caller-owned tensor of `rank` (1..5)
+ * dimensions. dims[0] is the innermost (contiguous) dimension;
+ * strides_bytes[i] is the byte stride of dimension i+1 (rank-1 entries,
+ * multiples of 16); box[i] is the tile extent per dimension. No counterpart
+ * in the reference, whose runner protocol cannot pass a descriptor
+ * (docs/DESIGN.md:860-863) and whose copy-engine path is therefore the
+ * untiled cp.async.bulk (emmy_ptx/bulk.py:34-57); here the descriptor is an
+ * extra kernel parameter listed in the module's launch header. */
+int emb_tensor_map(void* map_out, const void* base, int dtype, int rank, const uint64_t* dims,
+                   const uint64_t* strides_bytes, const uint32_t* box, int swizzle);
+
+/* Text of the last error on the calling thread ("" if none). */
+const char* emb_last_error(void);
+
+/* ABI version of this header. */
+int emb_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EMMY_B200_H */
