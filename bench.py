@@ -1,0 +1,312 @@
+#!/usr/bin/env python3
+"""Benchmark of the hot path: one pass of a workload's kernel chain per step, on 1..8 GPUs.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload softmax|sum|...] [--mode optimized|strict]
+    python bench.py --impl reference ...      # the CPU interpreter of the same IR on the host cores
+
+One JSON line on stdout (rank 0). ``value`` is microseconds per pass of the workload's kernel
+chain with the inputs resident in HBM (CUDA events on the launching stream, L2 flushed between
+passes, max over ranks); ``e2e`` is the same pass through the public API from HOST buffers
+(pinned host -> device copy of the inputs, the launches, device -> host copy of the result, all
+inside the event pair); ``roofline`` is the dominant kernel's algorithmic bytes per launch over
+its measured duration against the measured HBM peak; ``cpu_baseline`` is the oracle (a port of the
+reference's numpy interpreter) timed on a bounded sample of the same workload.
+
+Multi-GPU: launched by torchrun with one rank per GPU. The workloads shard without any data-path
+exchange (rows, batch*heads, element ranges), every rank runs the full single-GPU workload on its
+own shard of an N-times larger job (weak scaling); the array sum adds its one exchange, an NCCL
+all-reduce of the per-GPU scalar.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+PKG = ROOT / "emmy-ptx-compiler_b200"
+for p in (PKG, ROOT):
+    if str(p) not in sys.path:
+        sys.path.insert(0, str(p))
+
+WORKLOADS = {
+    # name: (problem folder, algorithmic bytes of the dominant kernel per launch, unit work for the tensor ones)
+    "softmax": dict(folder="f_softmax_8192x4096", bound="hbm", bytes=2 * 8192 * 4096 * 4, dominant=0, dtype="f32",
+                    describe="row softmax [8192,4096] f32 (BASELINE configs[1])"),
+    "sum": dict(folder="r_sum_16m", bound="hbm", bytes=(1 << 24) * 4, dominant=0, dtype="f32",
+                describe="f32 array sum of 2^24 (BASELINE configs[0]): block partials + final fold"),
+    "matmul": dict(folder="m_f16_8192", bound="tensor", flops=2 * 8192 ** 3, dominant=0, dtype="f16",
+                   describe="f16 GEMM 8192^3, f32 accumulate (BASELINE configs[2])"),
+    "attention": dict(folder="a_f16_causal_8x32x4096x128", bound="tensor", flops=4 * 8 * 32 * 128 * 4096 * 4097 // 2,
+                      dominant=0, dtype="f16", describe="causal attention 8x32x4096x128 f16 (BASELINE configs[3])"),
+    "mlp": dict(folder="k_mlp_gelu_tanh_16384x4096x16384", bound="tensor", flops=2 * 2 * 16384 * 4096 * 16384, dominant=0,
+                dtype="bf16", describe="fused GELU MLP 16384x4096x16384, bf16 x, e4m3 weights (BASELINE configs[4])"),
+}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
+# captures summarised under profiles/ (None until captured)
+NCU_TRAFFIC = {"softmax": None, "sum": None}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks() -> tuple:
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        d = json.loads(f.read_text())
+        return d, "measured"
+    return FALLBACK_PEAKS, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and clock-event reasons through NVML while the timed region runs (read only)."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting"}
+
+    def __init__(self, device: int):
+        super().__init__(daemon=True)
+        self.samples, self.reasons, self.max_mhz, self.ok = [], set(), None, False
+        self.stop_flag = threading.Event()
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            try:
+                uuid = str(torch.cuda.get_device_properties(device).uuid)
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode() if not uuid.startswith("GPU-") else uuid.encode())
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(device)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        while not self.stop_flag.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                get = getattr(self.nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                    self.nv.nvmlDeviceGetCurrentClocksThrottleReasons
+                bits = get(self.h)
+                for bit, name in self.REASONS.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def result(self) -> dict:
+        self.stop_flag.set()
+        if self.is_alive():
+            self.join(timeout=1)
+        if not self.samples:
+            return dict(sm_mhz=None, sm_max_mhz=self.max_mhz, reasons=sorted(self.reasons), samples=0)
+        return dict(sm_mhz=statistics.median(self.samples), sm_max_mhz=self.max_mhz, reasons=sorted(self.reasons),
+                    samples=len(self.samples))
+
+
+def oracle_sample(workload: str, budget_s: float, workers: int) -> dict:
+    """Time the oracle on a bounded sample of the workload's blocks and extrapolate to the grid."""
+    import numpy as np
+    from emmy_ptx import problems, runner
+    from oracle import ir_oracle
+    make = problems.WORKLOADS[workload]
+    p = make()
+    meta_args = json.loads((PKG / "problems" / WORKLOADS[workload]["folder"] / "meta.json").read_text())["kernels"]
+    total_us, notes = 0.0, []
+    host = None
+    for kern, km in zip(p["kernels"], meta_args):
+        grid, block = kern["grid"], kern["block"]
+        # inputs: small synthetic stand-ins of the right shapes are not enough for the interpreter (it indexes the
+        # real buffers), so the real host inputs are generated once
+        if host is None:
+            host = runner.host_inputs(km["args"])
+        bufs = dict(host)
+        name, shape, dt = kern["output"]
+        bufs[name] = np.zeros(shape, runner.numpy_dtype(dt))
+        for k2 in p["kernels"]:
+            n2, s2, d2 = k2["output"]
+            bufs.setdefault(n2, np.zeros(s2, runner.numpy_dtype(d2)))
+        probe = max(1, min(grid, 4))
+        t0 = time.perf_counter()
+        ir_oracle.run(kern["body"], bufs, grid, block, blocks=range(probe))
+        per_block = (time.perf_counter() - t0) / probe
+        sample = int(max(probe, min(grid, budget_s / max(per_block, 1e-9) / len(p["kernels"]))))
+        step = max(1, grid // sample)
+        blocks = list(range(0, grid, step))[:sample]
+        t0 = time.perf_counter()
+        ir_oracle.run(kern["body"], bufs, grid, block, blocks=blocks)
+        dt_s = time.perf_counter() - t0
+        total_us += dt_s / len(blocks) * grid * 1e6
+        notes.append(f"{kern['entry']}: {len(blocks)} of {grid} CTAs interpreted in {dt_s:.1f} s, scaled to the grid")
+    return dict(value=total_us, unit="us", cores=1, kind="port", sample="; ".join(notes) +
+                " (oracle/ir_oracle.py, numpy, one thread; extrapolated)")
+
+
+def reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w = WORKLOADS[args.workload]
+    steps = max(1, args.steps)
+    vals = []
+    base = None
+    for _ in range(min(steps, 3)):  # each step is a bounded sample; more than a few repeats adds nothing
+        base = oracle_sample(args.workload, budget_s=8.0, workers=1)
+        vals.append(base["value"])
+    value = statistics.median(vals)
+    base["value"] = value
+    line = dict(impl="reference", metric="us_per_kernel", value=value, unit="us", n_gpus=args.gpus, steps=len(vals),
+                warmup=0, ms_per_step=value / 1000.0, higher_is_better=False, scaling="weak", vs_baseline=None,
+                dtype=w["dtype"], data="synthetic", config=dict(workload=w["describe"], l2="n/a (CPU)"),
+                cpu_baseline=base, e2e=dict(value=value, unit="us", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default="softmax", choices=sorted(WORKLOADS))
+    ap.add_argument("--mode", default="optimized", choices=("optimized", "strict"))
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--families", default="sum", help="comma-separated extra workloads measured after the headline one")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    from emmy_ptx import driver, runner
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the kernels run on the GPU only")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    warmup = max(args.warmup, 3)
+    pk, pk_kind = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # larger than the 126 MB L2
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def measure(workload: str, steps: int, with_e2e: bool):
+        w = WORKLOADS[workload]
+        prob = runner.Problem(PKG / "problems" / w["folder"], args.mode, device=local)
+        stream = prob.stream
+        extra = None
+        if workload == "sum" and world > 1:
+            extra = prob.tensors["sum_1"]
+        # warm-up, then the timed region: barrier + synchronize on both sides
+        us_all = []
+        barrier()
+        if extra is None:
+            us_all = prob.time_us(warmup=warmup, iters=steps, flush=(flush.data_ptr(), flush.numel()))
+        else:  # the one real exchange: all-reduce of the per-GPU scalar, inside the step
+            for i in range(warmup + steps):
+                flush.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                driver.launch(prob.launches, stream)
+                dist.all_reduce(extra)
+                b.record()
+                b.synchronize()
+                if i >= warmup:
+                    us_all.append(a.elapsed_time(b) * 1000.0)
+        barrier()
+        total = torch.tensor([sum(us_all)], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(total, op=dist.ReduceOp.MAX)
+        mean_us = float(total.item()) / steps
+        # the dominant kernel alone, for the roofline
+        dom = prob.launches[w["dominant"]]
+        dom_us = statistics.mean(driver.time_chain([dom], stream, 3, max(10, min(steps, 50)), (flush.data_ptr(), flush.numel())))
+        if w["bound"] == "hbm":
+            achieved = w["bytes"] / dom_us / 1e3  # GB/s
+            peak, unit = float(pk["hbm_gbs"]), "GB/s"
+        else:
+            achieved = w["flops"] / dom_us / 1e6  # TFLOP/s
+            peak, unit = float(pk["bf16_tflops"]), "TFLOP/s"
+        roof = dict(bound=w["bound"], achieved=achieved, peak=peak, unit=unit, frac=achieved / peak,
+                    traffic=NCU_TRAFFIC.get(workload), kernel=prob.kernels[w["dominant"]].meta["entry"], kernel_us=dom_us,
+                    peak_source=f"of {pk_kind}", family=prob.kernels[w["dominant"]].launch_info.get("family"))
+        e2e = None
+        if with_e2e:
+            ins = {n: prob.tensors[n] for n in prob.host}
+            pinned = {n: torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True).copy_(t.cpu()) for n, t in ins.items()}
+            outs = [a["name"] for a in prob.meta["kernels"][-1]["args"] if a.get("output")]
+            out_host = {n: torch.empty(prob.tensors[n].shape, dtype=prob.tensors[n].dtype, device="cpu", pin_memory=True) for n in outs}
+            h2d = sum(t.numel() * t.element_size() for t in pinned.values())
+            d2h = sum(t.numel() * t.element_size() for t in out_host.values())
+            reps = max(3, min(steps, 10))
+            times = []
+            barrier()
+            for i in range(2 + reps):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for n, t in pinned.items():
+                    ins[n].copy_(t, non_blocking=True)
+                driver.launch(prob.launches, stream)
+                for n in outs:
+                    out_host[n].copy_(prob.tensors[n], non_blocking=True)
+                b.record()
+                b.synchronize()
+                if i >= 2:
+                    times.append(a.elapsed_time(b) * 1000.0)
+            barrier()
+            t_e2e = torch.tensor([statistics.mean(times)], dtype=torch.float64, device="cuda")
+            if world > 1:
+                dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
+            e2e = dict(value=float(t_e2e.item()), unit="us", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h)
+        return prob, mean_us, statistics.median(us_all), roof, e2e
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    prob, mean_us, median_us, roof, e2e = measure(args.workload, args.steps, True)
+    clocks = sampler.result()
+    w = WORKLOADS[args.workload]
+    launches = args.steps * prob.launch_count()
+
+    families = []
+    for name in [f for f in args.families.split(",") if f and f != args.workload and f in WORKLOADS]:
+        try:
+            fp, f_mean, f_med, f_roof, _ = measure(name, min(args.steps, 30), False)
+            families.append(dict(workload=WORKLOADS[name]["describe"], us_per_pass=f_mean, median_us=f_med, roofline=f_roof,
+                                 kernels=[k.meta["entry"] for k in fp.kernels]))
+        except Exception as e:  # an extra line must not cost the headline one
+            families.append(dict(workload=name, error=f"{type(e).__name__}: {e}"[:300]))
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = oracle_sample(args.workload, budget_s=12.0, workers=1)
+    if rank == 0:
+        line = dict(metric="us_per_kernel", value=mean_us, unit="us", n_gpus=world, steps=args.steps, warmup=warmup,
+                    ms_per_step=mean_us / 1000.0, higher_is_better=False, scaling="weak", vs_baseline=None, dtype=w["dtype"],
+                    data="synthetic", median_us=median_us,
+                    config=dict(workload=w["describe"], mode=args.mode, l2="flushed between timed passes (256 MiB memset)",
+                                sharding="each rank runs the full workload on its own rows/elements"),
+                    roofline=roof, cpu_baseline=cpu, e2e=e2e, gpu_launches=launches, clocks=clocks, families=families,
+                    aggregate=dict(value=(w.get("bytes", 0) * world / mean_us / 1e3) if w["bound"] == "hbm" else
+                                   (w["flops"] * world / mean_us / 1e6), unit="GB/s" if w["bound"] == "hbm" else "TFLOP/s"))
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,49 @@
+"""libemmyb200.so loads without a GPU and exports every symbol include/emmy_b200.h declares."""
+
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import __graft_entry__ as g
+    return ctypes.CDLL(str(g.build_library()))
+
+
+def declared_functions():
+    text = (ROOT / "include" / "emmy_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(emb_\w+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = declared_functions()
+    assert "emb_launch" in names and "emb_tensor_map" in names and len(names) >= 10
+    for n in names:
+        assert hasattr(lib, n), n
+
+
+def test_calls_fail_loudly_without_a_driver_or_with_bad_arguments(lib):
+    lib.emb_last_error.restype = ctypes.c_char_p
+    assert lib.emb_abi_version() == 1
+    code = lib.emb_init(0)
+    if code == -1:  # this machine has no CUDA driver: every call says so instead of computing anything
+        assert b"libcuda" in lib.emb_last_error()
+        assert lib.emb_launch(None, None) == -1
+    else:
+        assert lib.emb_launch(None, None) == -2 and b"null" in lib.emb_last_error()
+
+
+def test_product_path_refuses_to_run_without_a_gpu(tmp_path):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    from emmy_ptx import driver, problems, runner
+    folder = problems.write(problems.array_sum(n=4096, grid=4, block=128, final_block=64, ident="t"), tmp_path)
+    with pytest.raises(driver.EmbError):
+        runner.Problem(folder)
