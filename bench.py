@@ -5,8 +5,9 @@
     python bench.py --impl reference ...      # the CPU interpreter of the same IR on the host cores
 
 One JSON line on stdout (rank 0). ``value`` is microseconds per pass of the workload's kernel
-chain with the inputs resident in HBM (CUDA events on the launching stream, L2 flushed between
-passes, max over ranks); ``e2e`` is the same pass through the public API from HOST buffers
+chain with the inputs resident in HBM: K passes back to back between one CUDA event pair on the
+launching stream, the passes rotating through enough copies of every buffer that none finds its
+data in L2, max over ranks; ``e2e`` is the same pass through the public API from HOST buffers
 (pinned host -> device copy of the inputs, the launches, device -> host copy of the result, all
 inside the event pair); ``roofline`` is the dominant kernel's algorithmic bytes per launch over
 its measured duration against the measured HBM peak; ``cpu_baseline`` is the oracle (a port of the
@@ -198,7 +199,6 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     warmup = max(args.warmup, 3)
     pk, pk_kind = peaks()
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # larger than the 126 MB L2
 
     def barrier():
         if world > 1:
@@ -209,33 +209,33 @@ def main() -> None:
         w = WORKLOADS[workload]
         prob = runner.Problem(PKG / "problems" / w["folder"], args.mode, device=local)
         stream = prob.stream
-        extra = None
-        if workload == "sum" and world > 1:
-            extra = prob.tensors["sum_1"]
-        # warm-up, then the timed region: barrier + synchronize on both sides
-        us_all = []
+        nsets = prob.rotate(min_bytes=512 << 20)  # the buffer sets together exceed the 126 MB L2: every pass is cold
+        set_bytes = sum(t.numel() * t.element_size() for t in prob.tensors.values())
+        exchange = workload == "sum" and world > 1
         barrier()
-        if extra is None:
-            us_all = prob.time_us(warmup=warmup, iters=steps, flush=(flush.data_ptr(), flush.numel()))
-        else:  # the one real exchange: all-reduce of the per-GPU scalar, inside the step
-            for i in range(warmup + steps):
-                flush.zero_()
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                driver.launch(prob.launches, stream)
-                dist.all_reduce(extra)
-                b.record()
-                b.synchronize()
-                if i >= warmup:
-                    us_all.append(a.elapsed_time(b) * 1000.0)
+        if not exchange:
+            total_us = prob.time_rotating_us(warmup=warmup, iters=1, batch=steps)[0] * steps
+        else:  # the one real exchange of the path: an all-reduce of the per-GPU scalar, inside every step
+            finals = [prob.tensors["sum_1"]] + [c["sum_1"] for c in prob.copies]
+            for i in range(warmup):
+                driver.launch(prob.sets[i % nsets], stream)
+                dist.all_reduce(finals[i % nsets])
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for i in range(warmup, warmup + steps):
+                driver.launch(prob.sets[i % nsets], stream)
+                dist.all_reduce(finals[i % nsets])
+            b.record()
+            b.synchronize()
+            total_us = a.elapsed_time(b) * 1000.0
         barrier()
-        total = torch.tensor([sum(us_all)], dtype=torch.float64, device="cuda")
+        total = torch.tensor([total_us], dtype=torch.float64, device="cuda")
         if world > 1:
             dist.all_reduce(total, op=dist.ReduceOp.MAX)
         mean_us = float(total.item()) / steps
-        # the dominant kernel alone, for the roofline
-        dom = prob.launches[w["dominant"]]
-        dom_us = statistics.mean(driver.time_chain([dom], stream, 3, max(10, min(steps, 50)), (flush.data_ptr(), flush.numel())))
+        per_launch = prob.time_rotating_us(warmup=3, iters=max(10, min(steps, 50)), batch=1)  # one event pair per pass
+        # the dominant kernel alone over the same kind of timed region, for the roofline
+        dom_us = prob.time_rotating_us(warmup=warmup, iters=1, batch=steps, only=w["dominant"])[0]
         if w["bound"] == "hbm":
             achieved = w["bytes"] / dom_us / 1e3  # GB/s
             peak, unit = float(pk["hbm_gbs"]), "GB/s"
@@ -245,6 +245,7 @@ def main() -> None:
         roof = dict(bound=w["bound"], achieved=achieved, peak=peak, unit=unit, frac=achieved / peak,
                     traffic=NCU_TRAFFIC.get(workload), kernel=prob.kernels[w["dominant"]].meta["entry"], kernel_us=dom_us,
                     peak_source=f"of {pk_kind}", family=prob.kernels[w["dominant"]].launch_info.get("family"))
+        timing = dict(buffer_sets=nsets, bytes_per_set=set_bytes, us_per_pass_with_an_event_pair_each=statistics.median(per_launch))
         e2e = None
         if with_e2e:
             ins = {n: prob.tensors[n] for n in prob.host}
@@ -273,11 +274,11 @@ def main() -> None:
             if world > 1:
                 dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
             e2e = dict(value=float(t_e2e.item()), unit="us", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h)
-        return prob, mean_us, statistics.median(us_all), roof, e2e
+        return prob, mean_us, timing, roof, e2e
 
     sampler = ClockSampler(local)
     sampler.start()
-    prob, mean_us, median_us, roof, e2e = measure(args.workload, args.steps, True)
+    prob, mean_us, timing, roof, e2e = measure(args.workload, args.steps, True)
     clocks = sampler.result()
     w = WORKLOADS[args.workload]
     launches = args.steps * prob.launch_count()
@@ -286,7 +287,7 @@ def main() -> None:
     for name in [f for f in args.families.split(",") if f and f != args.workload and f in WORKLOADS]:
         try:
             fp, f_mean, f_med, f_roof, _ = measure(name, min(args.steps, 30), False)
-            families.append(dict(workload=WORKLOADS[name]["describe"], us_per_pass=f_mean, median_us=f_med, roofline=f_roof,
+            families.append(dict(workload=WORKLOADS[name]["describe"], us_per_pass=f_mean, timing=f_med, roofline=f_roof,
                                  kernels=[k.meta["entry"] for k in fp.kernels]))
         except Exception as e:  # an extra line must not cost the headline one
             families.append(dict(workload=name, error=f"{type(e).__name__}: {e}"[:300]))
@@ -297,8 +298,10 @@ def main() -> None:
     if rank == 0:
         line = dict(metric="us_per_kernel", value=mean_us, unit="us", n_gpus=world, steps=args.steps, warmup=warmup,
                     ms_per_step=mean_us / 1000.0, higher_is_better=False, scaling="weak", vs_baseline=None, dtype=w["dtype"],
-                    data="synthetic", median_us=median_us,
-                    config=dict(workload=w["describe"], mode=args.mode, l2="flushed between timed passes (256 MiB memset)",
+                    data="synthetic", timing=timing,
+                    config=dict(workload=w["describe"], mode=args.mode,
+                                l2=f"inputs larger than L2: passes rotate through {timing['buffer_sets']} buffer sets of "
+                                   f"{timing['bytes_per_set'] >> 20} MiB, no flush",
                                 sharding="each rank runs the full workload on its own rows/elements"),
                     roofline=roof, cpu_baseline=cpu, e2e=e2e, gpu_launches=launches, clocks=clocks, families=families,
                     aggregate=dict(value=(w.get("bytes", 0) * world / mean_us / 1e3) if w["bound"] == "hbm" else

@@ -124,16 +124,25 @@ int launch_one(const emb_launch_t& k, CUstream stream) {
     cfg.blockDimX = k.block[0], cfg.blockDimY = k.block[1], cfg.blockDimZ = k.block[2];
     cfg.sharedMemBytes = k.smem_bytes;
     cfg.hStream = stream;
-    CUlaunchAttribute attr[1];
+    CUlaunchAttribute attr[2];
+    unsigned nattr = 0;
+    if (k.flags & EMB_LAUNCH_PDL) {
+        attr[nattr].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+        attr[nattr].value.programmaticStreamSerializationAllowed = 1;
+        ++nattr;
+    }
     if (k.cluster_x > 1) {
         if (k.grid[0] % k.cluster_x) return fail(EMB_E_ARGUMENT, "launch: grid %u is not a multiple of the cluster size %u",
                                                  k.grid[0], k.cluster_x);
-        attr[0].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
-        attr[0].value.clusterDim.x = k.cluster_x;
-        attr[0].value.clusterDim.y = 1;
-        attr[0].value.clusterDim.z = 1;
+        attr[nattr].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+        attr[nattr].value.clusterDim.x = k.cluster_x;
+        attr[nattr].value.clusterDim.y = 1;
+        attr[nattr].value.clusterDim.z = 1;
+        ++nattr;
+    }
+    if (nattr) {
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = nattr;
     }
     return check(g_drv.LaunchKernelEx(&cfg, fn, k.params, nullptr), "cuLaunchKernelEx");
 }
@@ -142,7 +151,7 @@ int launch_one(const emb_launch_t& k, CUstream stream) {
 
 extern "C" {
 
-int emb_abi_version(void) { return 1; }
+int emb_abi_version(void) { return 2; }
 
 const char* emb_last_error(void) { return g_error; }
 
@@ -241,6 +250,35 @@ int emb_time_chain(const emb_launch_t* launches, int n, void* stream, int warmup
         float ms = 0.f;
         r = check(g_drv.EventElapsedTime(&ms, ev[2 * i], ev[2 * i + 1]), "cuEventElapsedTime");
         us_out[i] = ms * 1000.f;
+    }
+    for (auto& e : ev)
+        if (e) g_drv.EventDestroy(e);
+    return r;
+}
+
+int emb_time_rotating(const emb_launch_t* launches, int chain_len, int n_sets, void* stream, int warmup, int iters,
+                      int batch, float* us_out) {
+    NEED_DRIVER();
+    if (!launches || chain_len <= 0 || n_sets <= 0 || iters <= 0 || warmup < 0 || batch <= 0 || !us_out)
+        return fail(EMB_E_ARGUMENT, "time_rotating: bad chain, counts or output");
+    CUstream s = static_cast<CUstream>(stream);
+    std::vector<CUevent> ev(2 * static_cast<size_t>(iters), nullptr);
+    int r = 0;
+    for (auto& e : ev)
+        if ((r = check(g_drv.EventCreate(&e, CU_EVENT_DEFAULT), "cuEventCreate"))) break;
+    int run = 0;
+    for (int i = 0; !r && i < warmup; ++i, ++run) r = emb_launch_chain(launches + (run % n_sets) * chain_len, chain_len, stream);
+    for (int i = 0; !r && i < iters; ++i) {
+        r = check(g_drv.EventRecord(ev[2 * i], s), "cuEventRecord");
+        for (int b = 0; !r && b < batch; ++b, ++run)
+            r = emb_launch_chain(launches + (run % n_sets) * chain_len, chain_len, stream);
+        if (!r) r = check(g_drv.EventRecord(ev[2 * i + 1], s), "cuEventRecord");
+    }
+    if (!r) r = check(g_drv.StreamSynchronize(s), "cuStreamSynchronize");
+    for (int i = 0; !r && i < iters; ++i) {
+        float ms = 0.f;
+        r = check(g_drv.EventElapsedTime(&ms, ev[2 * i], ev[2 * i + 1]), "cuEventElapsedTime");
+        us_out[i] = ms * 1000.f / static_cast<float>(batch);
     }
     for (auto& e : ev)
         if (e) g_drv.EventDestroy(e);

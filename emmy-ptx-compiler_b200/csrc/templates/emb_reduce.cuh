@@ -70,53 +70,45 @@ template <class Op, int LEN> __device__ __forceinline__ float tree_fold(const fl
 }
 
 // Per-thread fold of x[i + j], j < VEC, for i = start, start + step, ... < end.
+//
+// The trips are taken UNROLL at a time with every load of the round issued before the first
+// add (a thread keeps UNROLL * VEC * 4 bytes in flight); trips past `end` are predicated off, so
+// a ragged last round costs no serial tail. STRICT: one accumulator, the IR's order (a skipped
+// trip adds nothing, not even a zero). Otherwise UNROLL * VEC independent accumulators, merged
+// at the end.
 template <int VEC, class Fold, int UNROLL, bool STRICT>
 __device__ __forceinline__ float strided_fold(const float* __restrict__ x, long long start, long long step, long long end) {
-    long long i = start;
-    if (STRICT) {
-        // one accumulator, the IR's order; the loads of UNROLL trips are in flight together
-        float acc = Fold::identity();
-        for (; i + (UNROLL - 1) * step < end; i += UNROLL * step) {
-            Vec<VEC> v[UNROLL];
+    float a[STRICT ? 1 : UNROLL][STRICT ? 1 : VEC];
 #pragma unroll
-            for (int u = 0; u < UNROLL; ++u) v[u] = load_stream<VEC>(x + i + u * step);
+    for (int u = 0; u < (STRICT ? 1 : UNROLL); ++u)
 #pragma unroll
-            for (int u = 0; u < UNROLL; ++u)
-#pragma unroll
-                for (int j = 0; j < VEC; ++j) acc = Fold::apply(acc, v[u].v[j]);
-        }
-        for (; i < end; i += step) {
-            Vec<VEC> v = load_stream<VEC>(x + i);
-#pragma unroll
-            for (int j = 0; j < VEC; ++j) acc = Fold::apply(acc, v.v[j]);
-        }
-        return acc;
-    }
-    float a[UNROLL][VEC];
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u)
-#pragma unroll
-        for (int j = 0; j < VEC; ++j) a[u][j] = Fold::identity();
-    for (; i + (UNROLL - 1) * step < end; i += UNROLL * step) {
+        for (int j = 0; j < (STRICT ? 1 : VEC); ++j) a[u][j] = Fold::identity();
+    for (long long i = start; i < end; i += UNROLL * step) {
         Vec<VEC> v[UNROLL];
+        bool ok[UNROLL];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) v[u] = load_stream<VEC>(x + i + u * step);
+        for (int u = 0; u < UNROLL; ++u) {
+            ok[u] = i + u * step < end;
+            if (ok[u]) v[u] = load_stream<VEC>(x + i + u * step);
+        }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u)
+            if (ok[u]) {
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) a[u][j] = Fold::apply(a[u][j], v[u].v[j]);
+                for (int j = 0; j < VEC; ++j) {
+                    float& acc = a[STRICT ? 0 : u][STRICT ? 0 : j];
+                    acc = Fold::apply(acc, v[u].v[j]);
+                }
+            }
     }
-    for (; i < end; i += step) {
-        Vec<VEC> v = load_stream<VEC>(x + i);
+    if (!STRICT) {
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) a[0][j] = Fold::apply(a[0][j], v.v[j]);
+        for (int u = 1; u < UNROLL; ++u)
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) a[0][j] = Fold::apply(a[0][j], a[u][j]);
+#pragma unroll
+        for (int j = 1; j < VEC; ++j) a[0][0] = Fold::apply(a[0][0], a[0][j]);
     }
-#pragma unroll
-    for (int u = 1; u < UNROLL; ++u)
-#pragma unroll
-        for (int j = 0; j < VEC; ++j) a[0][j] = Fold::apply(a[0][j], a[u][j]);
-#pragma unroll
-    for (int j = 1; j < VEC; ++j) a[0][0] = Fold::apply(a[0][0], a[0][j]);
     return a[0][0];
 }
 

@@ -676,6 +676,30 @@ template <class T> __device__ __forceinline__ T zero() { return T(0); }
 """
 
 
+def dependent_launch(src) -> tuple:
+    """(waits, triggers): does the kernel read another kernel's ``intermediate`` output, and is its
+    own output one (``final`` false)? From meta.json (examples/m_f16_128/meta.json shows the chain)."""
+    meta = getattr(src, "meta", None)
+    if not meta:
+        return False, False
+    waits = any(a.get("intermediate") for a in meta.get("args", ()))
+    return waits, not meta.get("final", True)
+
+
+def pdl_prologue(src, enabled: bool) -> list:
+    """Programmatic dependent launch: let the next kernel of the chain be scheduled now, and wait for
+    the previous one before touching its results."""
+    if not enabled:
+        return []
+    waits, triggers = dependent_launch(src)
+    out = []
+    if triggers:
+        out.append('    asm volatile("griddepcontrol.launch_dependents;");')
+    if waits:
+        out.append('    asm volatile("griddepcontrol.wait;" ::: "memory");')
+    return out
+
+
 def generate(src, plain: bool = False, strict: bool = False) -> tuple:
     """(CUDA source, remarks) of the statement-by-statement lowering of ``src``."""
     em = Emitter(src, plain, strict)
@@ -686,5 +710,5 @@ def generate(src, plain: bool = False, strict: bool = False) -> tuple:
             f'extern "C" __global__ void __launch_bounds__({src.launch.block}) {src.name}({signature(src)}) {{',
             "    const unsigned emb_warp = __activemask();",
             "    int v_lane = threadIdx.x & 31, v_warp = threadIdx.x >> 5;",
-            "    (void)emb_warp; (void)v_lane; (void)v_warp;"]
+            "    (void)emb_warp; (void)v_lane; (void)v_warp;"] + pdl_prologue(src, not plain)
     return "\n".join(head + smem + decls + em.lines + ["}"]) + "\n", em.remarks

@@ -27,7 +27,9 @@ class EmbError(RuntimeError):
 class LaunchDesc(ctypes.Structure):
     _fields_ = [("fn", ctypes.c_void_p), ("grid", ctypes.c_uint32 * 3), ("block", ctypes.c_uint32 * 3),
                 ("cluster_x", ctypes.c_uint32), ("smem_bytes", ctypes.c_uint32),
-                ("params", ctypes.POINTER(ctypes.c_void_p)), ("nparams", ctypes.c_int32)]
+                ("params", ctypes.POINTER(ctypes.c_void_p)), ("nparams", ctypes.c_int32), ("flags", ctypes.c_uint32)]
+
+LAUNCH_PDL = 1
 
 
 _lib = None
@@ -49,6 +51,8 @@ def library() -> ctypes.CDLL:
         lib.emb_launch_chain.argtypes = [ctypes.POINTER(LaunchDesc), ctypes.c_int, ctypes.c_void_p]
         lib.emb_time_chain.argtypes = [ctypes.POINTER(LaunchDesc), ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
                                        ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_float)]
+        lib.emb_time_rotating.argtypes = [ctypes.POINTER(LaunchDesc), ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                                          ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_float)]
         lib.emb_tensor_map.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
                                        ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64),
                                        ctypes.POINTER(ctypes.c_uint32), ctypes.c_int]
@@ -113,7 +117,7 @@ class TensorMap:
 class Launch:
     """One kernel launch with its parameter storage kept alive."""
 
-    def __init__(self, fn: Function, grid, block, cluster: int, smem_bytes: int, params: list):
+    def __init__(self, fn: Function, grid, block, cluster: int, smem_bytes: int, params: list, flags: int = 0):
         """``params``: an int (a device pointer) or a TensorMap per kernel parameter."""
         self.fn = fn
         self._keep = []
@@ -128,7 +132,7 @@ class Launch:
                 self._keep.append(cell)
                 self._slots[i] = ctypes.addressof(cell)
         self.desc = LaunchDesc(fn.handle, (ctypes.c_uint32 * 3)(*grid), (ctypes.c_uint32 * 3)(*block), int(cluster),
-                               int(smem_bytes), ctypes.cast(self._slots, ctypes.POINTER(ctypes.c_void_p)), n)
+                               int(smem_bytes), ctypes.cast(self._slots, ctypes.POINTER(ctypes.c_void_p)), n, int(flags))
 
 
 def _chain(launches):
@@ -153,4 +157,15 @@ def time_chain(launches, stream: int = 0, warmup: int = 3, iters: int = 20, flus
     ptr, size = flush if flush else (0, 0)
     check(library().emb_time_chain(_chain(launches), len(launches), ctypes.c_void_p(stream), warmup, iters,
                                    ctypes.c_void_p(ptr), size, out))
+    return list(out)
+
+
+def time_rotating(sets, stream: int = 0, warmup: int = 3, iters: int = 20, batch: int = 1) -> list:
+    """Microseconds per run of each of ``iters`` batches of ``batch`` consecutive runs, run i using
+    ``sets[i % len(sets)]`` (each a list of launches bound to its own buffers): with the sets
+    together larger than L2, every run is cold."""
+    sets = [list(s) for s in sets]
+    flat = [l for s in sets for l in s]
+    out = (ctypes.c_float * iters)()
+    check(library().emb_time_rotating(_chain(flat), len(sets[0]), len(sets), ctypes.c_void_p(stream), warmup, iters, batch, out))
     return list(out)

@@ -30,6 +30,11 @@ from . import codegen, ir
 from .codegen import CANON, CTYPE, Emitter, divisible
 from .ir import dtype_name, kind
 
+# Tunables of the reduction template (None: chosen from the kernel's shape).
+REDUCE_UNROLL = None      # trips of the strided fold in flight per round
+REDUCE_MIN_BLOCKS = None  # second argument of __launch_bounds__: caps registers so that many CTAs fit an SM
+MAX_FULL_UNROLL = 16      # a fold of at most this many trips is one fully unrolled, predicated round
+
 OP_TYPE = {"add": "emb::OpAdd", "multiply": "emb::OpMul", "maximum": "emb::OpMax", "minimum": "emb::OpMin"}
 
 
@@ -182,12 +187,13 @@ def tile_decode(em: Emitter, tile, block: int) -> None:
         stride *= n
 
 
-def finish(em: Emitter, src, includes: str, strict: bool, shared: list) -> str:
+def finish(em: Emitter, src, includes: str, strict: bool, shared: list, min_blocks=None) -> str:
     decls = [f"    {CTYPE[dt]} v_{n} = emb::zero<{CTYPE[dt]}>();" for n, dt in em.vars.items() if n not in ("lane", "warp")]
     head = [f"#define EMB_STRICT {int(strict)}", includes, codegen.PRELUDE.split("\n", 1)[1],
-            f'extern "C" __global__ void __launch_bounds__({src.launch.block}) {src.name}({codegen.signature(src)}) {{',
+            f'extern "C" __global__ void __launch_bounds__({src.launch.block}{f", {min_blocks}" if min_blocks else ""}) '
+            f'{src.name}({codegen.signature(src)}) {{',
             "    int v_lane = threadIdx.x & 31, v_warp = threadIdx.x >> 5;", "    (void)v_lane; (void)v_warp;",
-            "    const unsigned emb_warp = 0xffffffffu; (void)emb_warp;"]
+            "    const unsigned emb_warp = 0xffffffffu; (void)emb_warp;"] + codegen.pdl_prologue(src, True)
     return "\n".join(head + shared + decls + em.lines + ["}"]) + "\n"
 
 
@@ -244,7 +250,21 @@ def match_reduce(src, strict: bool) -> Plan:
     for s in ir.walk(tail):
         need(kind(s) in ("Cond", "Write", "Assign", "Let", "Load"), f"a {kind(s)} after the tree")
 
-    unroll = 4 if vec == 4 else 8
+    trips = None
+    if is_int(loop.step) and loop.end is None and loop.step.value > 0:
+        trips = -(-extent // loop.step.value)  # the most trips any thread takes
+    if REDUCE_UNROLL is not None:
+        unroll = REDUCE_UNROLL
+    elif trips is not None and trips <= MAX_FULL_UNROLL:
+        unroll = trips
+    else:
+        unroll = 8
+    min_blocks = REDUCE_MIN_BLOCKS
+    if min_blocks is None and src.launch.grid > TARGET_SMS:
+        # enough CTAs per SM for the whole grid to be resident at once, when the registers allow
+        per_sm = -(-src.launch.grid // TARGET_SMS)
+        if per_sm * block <= 2048 and 65536 // (per_sm * block) >= 24 + (1 if strict else unroll) * vec:
+            min_blocks = per_sm
     tree_op = OP_TYPE[comb.tree_op] if comb.tree_op else OP_TYPE[op]
     em.emit(f"float acc_ = emb::strided_fold<{vec}, {OP_TYPE[op]}, {unroll}, {str(bool(strict)).lower()}>("
             f"{pointer}, {start}, {step}, {end});")
@@ -253,8 +273,9 @@ def match_reduce(src, strict: bool) -> Plan:
     em.emit(f"{em.var(state, 'f32')} = acc_;")
     em.block(tail, None)
     shared = [f"    __shared__ float emb_slab[{max(comb.tree_len, 1)}];"]
-    source = finish(em, src, '#include "emb_reduce.cuh"', strict, shared)
+    source = finish(em, src, '#include "emb_reduce.cuh"', strict, shared, min_blocks)
     how = "in the IR's own order" if strict else f"on {unroll * vec} independent accumulators per thread"
+    how += f", {unroll} trips in flight per round"
     remarks = [f"block reduction template: {op} fold of {load.input} in {vec * 4}-byte ld.global.nc runs, {how}",
                f"butterfly over {comb.shuffle_len} lanes" +
                (f", then the {comb.tree_len} warps' partials folded in the tree's order by every thread behind one barrier"
@@ -269,6 +290,7 @@ def has_cross(stmts) -> bool:
 
 # ---------------------------------------------------------------- row softmax
 
+TARGET_SMS = 148
 MAX_ROW_VALUES = 64  # floats of the row one thread keeps in registers
 
 

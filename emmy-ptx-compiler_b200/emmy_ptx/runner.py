@@ -129,7 +129,8 @@ class CompiledKernel:
                                                p["box"], p.get("swizzle", "128B")))
             else:
                 raise ValueError(f"unknown parameter kind {p['kind']!r}")
-        return driver.Launch(self.function, li["grid"], li["block"], li.get("cluster", 1), li.get("smem_bytes", 0), params)
+        flags = driver.LAUNCH_PDL if li.get("pdl") else 0
+        return driver.Launch(self.function, li["grid"], li["block"], li.get("cluster", 1), li.get("smem_bytes", 0), params, flags)
 
 
 class Problem:
@@ -164,6 +165,7 @@ class Problem:
                     self.host[name] = given[name]
                     self.tensors[name] = to_torch(given[name], a["dtype"], self.device)
         self.launches = [k.bind(self.tensors) for k in self.kernels]
+        self.sets = [self.launches]  # further copies of every buffer, for cold-cache timing (rotate())
         self.zero = [n for k in self.meta["kernels"] for n in k.get("zero_outputs", ())]
 
     @property
@@ -186,6 +188,22 @@ class Problem:
 
     def time_us(self, warmup: int = 3, iters: int = 20, flush=None) -> list:
         return driver.time_chain(self.launches, self.stream, warmup, iters, flush)
+
+    def rotate(self, min_bytes: int = 512 << 20, max_sets: int = 16) -> int:
+        """Bind further copies of every tensor until the sets together hold ``min_bytes``:
+        timing then walks the sets, so a run never finds its data in the 126 MB L2."""
+        per_set = sum(t.numel() * t.element_size() for t in self.tensors.values())
+        want = max(2, min(max_sets, -(-min_bytes // max(per_set, 1))))
+        self.copies = getattr(self, "copies", [])
+        while len(self.sets) < want:
+            clone = {n: t.clone() for n, t in self.tensors.items()}
+            self.copies.append(clone)
+            self.sets.append([k.bind(clone) for k in self.kernels])
+        return len(self.sets)
+
+    def time_rotating_us(self, warmup: int = 3, iters: int = 20, only=None, batch: int = 1) -> list:
+        sets = self.sets if only is None else [[s[only]] for s in self.sets]
+        return driver.time_rotating(sets, self.stream, warmup, iters, batch)
 
     def launch_count(self) -> int:
         return len(self.launches)

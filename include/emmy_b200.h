@@ -56,7 +56,15 @@ typedef struct emb_launch_t {
     uint32_t smem_bytes; /* dynamic shared memory */
     void** params;
     int32_t nparams;
+    uint32_t flags; /* EMB_LAUNCH_* bits */
 } emb_launch_t;
+
+/* Programmatic dependent launch: the kernel may be scheduled while the kernel
+ * before it in the stream is still running, and itself waits
+ * (griddepcontrol.wait) before it touches that kernel's results. For a kernel
+ * whose inputs are another kernel's `intermediate` outputs (meta.json,
+ * tools/run_suite.py:81-85): hides the second launch's latency. */
+#define EMB_LAUNCH_PDL 1u
 
 /* Bind the calling thread to `device`'s primary context (retained once per
  * device). Must be called before the other functions; cheap to repeat. */
@@ -91,6 +99,17 @@ int emb_launch_chain(const emb_launch_t* launches, int n, void* stream);
  * timed run (outside the event pair) to evict the L2 cache. Synchronous. */
 int emb_time_chain(const emb_launch_t* launches, int n, void* stream, int warmup, int iters,
                    void* flush_ptr, size_t flush_bytes, float* us_out);
+
+/* The same, over `n_sets` copies of the chain bound to distinct buffers
+ * (`launches` holds n_sets * chain_len descriptors, set after set): run i uses
+ * set i % n_sets, so that with the sets together larger than the L2 cache
+ * every timed run reads its inputs from HBM without a flush in between. One
+ * event pair brackets `batch` consecutive runs (>= 1) and us_out[i] is that
+ * duration divided by `batch`: with a batch of many runs the events' own cost
+ * and the launch latency hidden behind the previous run drop out, which is how
+ * a stream of launches behaves in production. `iters` counts batches. */
+int emb_time_rotating(const emb_launch_t* launches, int chain_len, int n_sets, void* stream, int warmup, int iters,
+                      int batch, float* us_out);
 
 /* Build a tiled TMA descriptor (CUtensorMap, 128 bytes, 64-byte aligned
  * storage supplied by the caller) over a caller-owned tensor of `rank` (1..5)

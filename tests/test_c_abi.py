@@ -30,7 +30,7 @@ def test_every_declared_symbol_is_exported(lib):
 
 def test_calls_fail_loudly_without_a_driver_or_with_bad_arguments(lib):
     lib.emb_last_error.restype = ctypes.c_char_p
-    assert lib.emb_abi_version() == 1
+    assert lib.emb_abi_version() == 2
     code = lib.emb_init(0)
     if code == -1:  # this machine has no CUDA driver: every call says so instead of computing anything
         assert b"libcuda" in lib.emb_last_error()
