@@ -181,7 +181,7 @@ def main() -> None:
     ap.add_argument("--mode", default="optimized", choices=("optimized", "strict"))
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--families", default="sum", help="comma-separated extra workloads measured after the headline one")
+    ap.add_argument("--families", default="sum,matmul", help="comma-separated extra workloads measured after the headline one")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -209,7 +209,7 @@ def main() -> None:
         w = WORKLOADS[workload]
         prob = runner.Problem(PKG / "problems" / w["folder"], args.mode, device=local)
         stream = prob.stream
-        nsets = prob.rotate(min_bytes=512 << 20)  # the buffer sets together exceed the 126 MB L2: every pass is cold
+        nsets = prob.rotate(min_bytes=512 << 20, max_sets=8)  # the buffer sets together exceed the 126 MB L2: every pass is cold
         set_bytes = sum(t.numel() * t.element_size() for t in prob.tensors.values())
         exchange = workload == "sum" and world > 1
         barrier()
@@ -284,7 +284,7 @@ def main() -> None:
     launches = args.steps * prob.launch_count()
 
     families = []
-    for name in [f for f in args.families.split(",") if f and f != args.workload and f in WORKLOADS]:
+    for name in [f for f in args.families.split(",") if f and f != "none" and f != args.workload and f in WORKLOADS]:
         try:
             fp, f_mean, f_med, f_roof, _ = measure(name, min(args.steps, 30), False)
             families.append(dict(workload=WORKLOADS[name]["describe"], us_per_pass=f_mean, timing=f_med, roofline=f_roof,

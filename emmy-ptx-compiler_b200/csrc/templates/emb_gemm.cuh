@@ -1,0 +1,206 @@
+// Tensor-core matmul template for sm_100a: C[M,N] = A[M,K] * B[N,K]^T, A and B 16-bit (f16 or bf16),
+// both K-major ("row-major A, column-major B"), f32 accumulation in tensor memory, C rounded once to
+// the output type.
+//
+// It takes the place of the reference's tensor-core lowering, which turns emmy's fragment statements
+// into ldmatrix / mma.sync.m16n8k16 on 16x8 warp tiles (emmy_ptx/tensorcore.py:165-279,376-420) fed by
+// cp.async (emmy_ptx/lower.py:1057-1102) or, with --bulk-copy, by untiled cp.async.bulk on eight
+// round-robin mbarriers (emmy_ptx/bulk.py:34-57, emmy_ptx/lower.py:1167-1238). Here one persistent CTA
+// per SM walks 128 x 256 output tiles:
+//
+//   warp 0    producer  one thread issues TMA tensor-map loads of the A (128 x 64) and B (256 x 64)
+//                       K-slices into a ring of STAGES shared-memory stages; a stage's mbarrier counts
+//                       the bytes landed (full) and the MMAs that consumed it (empty)
+//   warp 1    MMA       one thread issues tcgen05.mma 128x256x16 (four per stage) accumulating into one
+//                       of two 256-column TMEM buffers; tcgen05.commit releases the stage and, after the
+//                       last K-slice, hands the buffer to the epilogue
+//   warps 2-5 epilogue  tcgen05.ld 32 lanes x 32 columns per warp, convert, 16-byte global stores; the
+//                       other TMEM buffer is being accumulated meanwhile
+//
+// No multicast, no clusters: every CTA loads its own tiles; reuse comes from L2 through the tile order
+// (GROUP_M row-blocks share each B panel while it is resident).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "emb_tc.cuh"
+
+namespace emb {
+
+template <bool BF16> struct Half16 { using type = __half; };
+template <> struct Half16<true> { using type = __nv_bfloat16; };
+
+template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<false>(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<true>(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+struct GemmShape {
+    int m, n, k;
+};
+
+template <int STAGES, int GROUP_M, bool BF16>
+__device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ map_a, const CUtensorMap* __restrict__ map_b,
+                                               void* __restrict__ c_out, GemmShape shape, unsigned* status) {
+    constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
+    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t TMEM_COLS = 512;
+    using out_t = typename Half16<BF16>::type;
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // the operand tiles need 1024-byte alignment for the 128-byte swizzle
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + STAGES;
+    uint64_t* tmem_full = bars + 2 * STAGES;
+    uint64_t* tmem_empty = bars + 2 * STAGES + 2;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+    const tc::Guard guard{status, abort_flag};
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (shape.m + BM - 1) / BM, tiles_n = (shape.n + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int k_blocks = (shape.k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            tc::mbar_init(&full[s], 1);
+            tc::mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            tc::mbar_init(&tmem_full[b], 1);
+            tc::mbar_init(&tmem_empty[b], 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        tc::mbar_init_fence();
+        tc::tma_prefetch_desc(map_a);
+        tc::tma_prefetch_desc(map_b);
+    }
+    if (warp == 1) tc::tmem_alloc(tmem_holder, TMEM_COLS);
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_holder;
+
+    // tile order: GROUP_M row-blocks at a time, all column-blocks under them, so that the CTAs running
+    // together share A and B panels in L2
+    auto tile_coords = [&](int t, int& tm, int& tn) {
+        const int per_group = GROUP_M * tiles_n;
+        const int g = t / per_group, r = t % per_group;
+        const int rows = min(GROUP_M, tiles_m - g * GROUP_M);
+        tm = g * GROUP_M + r % rows;
+        tn = r / rows;
+    };
+
+    if (warp == 0) {
+        if (tc::elect_one()) {
+            uint32_t it = 0;
+            bool alive = true;
+            for (int t = blockIdx.x; alive && t < num_tiles; t += gridDim.x) {
+                int tm, tn;
+                tile_coords(t, tm, tn);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                    if (!tc::mbar_wait(&empty[s], ph ^ 1, guard, tc::WAIT_SMEM_EMPTY, it)) {
+                        alive = false;
+                        break;
+                    }
+                    tc::mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+                    uint8_t* stage = smem + s * STAGE_BYTES;
+                    tc::tma_load_2d(stage, map_a, &full[s], kb * BK, tm * BM);
+                    tc::tma_load_2d(stage + A_BYTES, map_b, &full[s], kb * BK, tn * BN);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (tc::elect_one()) {
+            constexpr uint32_t idesc = tc::idesc_f16(BM, BN, BF16);
+            uint32_t it = 0, local = 0;
+            bool alive = true;
+            for (int t = blockIdx.x; alive && t < num_tiles; t += gridDim.x, ++local) {
+                const uint32_t buf = local & 1, use = local >> 1;
+                if (!tc::mbar_wait(&tmem_empty[buf], (use & 1) ^ 1, guard, tc::WAIT_TMEM_EMPTY, local)) break;
+                tc::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                    if (!tc::mbar_wait(&full[s], ph, guard, tc::WAIT_SMEM_FULL, it)) {
+                        alive = false;
+                        break;
+                    }
+                    tc::tc_fence_after_sync();
+                    const uint8_t* stage = smem + s * STAGE_BYTES;
+                    const uint64_t a_desc = tc::smem_desc_k128(stage), b_desc = tc::smem_desc_k128(stage + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        tc::mma_f16_ss(d_tmem, a_desc + (k * UMMA_K * 2 >> 4), b_desc + (k * UMMA_K * 2 >> 4), idesc,
+                                       (kb | k) != 0);
+                    tc::mma_commit(&empty[s]);  // the stage is free once these MMAs have read it
+                }
+                if (alive) tc::mma_commit(&tmem_full[buf]);
+            }
+        }
+    } else {
+        // epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
+        const int quarter = warp & 3;
+        uint32_t local = 0;
+        out_t* c = static_cast<out_t*>(c_out);
+        const bool vec_ok = (shape.n % 8) == 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
+            int tm, tn;
+            tile_coords(t, tm, tn);
+            const uint32_t buf = local & 1, use = local >> 1;
+            if (!tc::mbar_wait(&tmem_full[buf], use & 1, guard, tc::WAIT_TMEM_FULL, local)) break;
+            tc::tc_fence_after_sync();
+            const int row = tm * BM + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+            for (int cb = 0; cb < BN; cb += 32) {
+                uint32_t r[32];
+                tc::tmem_ld_32x32(taddr + cb, r);
+                tc::tmem_ld_wait();
+                const int col = tn * BN + cb;
+                if (row < shape.m) {
+                    out_t* dst = c + static_cast<size_t>(row) * shape.n + col;
+                    if (vec_ok && col + 32 <= shape.n) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint4 v;
+                            v.x = pack2<BF16>(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1]));
+                            v.y = pack2<BF16>(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]));
+                            v.z = pack2<BF16>(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
+                            v.w = pack2<BF16>(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
+                            *reinterpret_cast<uint4*>(dst + 8 * q) = v;
+                        }
+                    } else {
+                        for (int j = 0; j < 32; ++j)
+                            if (col + j < shape.n) {
+                                uint32_t p = pack2<BF16>(__uint_as_float(r[j]), 0.0f);
+                                dst[j] = *reinterpret_cast<out_t*>(&p);
+                            }
+                    }
+                }
+            }
+            tc::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&tmem_empty[buf]);
+        }
+    }
+
+    // teardown: everyone meets, then the allocating warp frees the tensor memory
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::tc_fence_after_sync();
+        tc::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace emb

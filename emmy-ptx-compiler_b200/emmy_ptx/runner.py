@@ -118,11 +118,21 @@ class CompiledKernel:
         self.function = self.module.function(meta["entry"])
 
     def bind(self, tensors: dict) -> driver.Launch:
+        """A launch of this kernel on ``tensors`` (name -> torch tensor). A ``status`` parameter (the
+        word a kernel's bounded waits report into) gets its own zeroed tensor, kept in ``tensors``
+        under ``"<entry>.status"`` and read by ``check_status``."""
+        import torch
         li = self.launch_info
         params = []
         for p in li["params"]:
             if p["kind"] == "buffer":
                 params.append(tensors[p["name"]].data_ptr())
+            elif p["kind"] == "status":
+                key = f"{self.meta['entry']}.status"
+                if key not in tensors:
+                    anchor = next(iter(tensors.values()))
+                    tensors[key] = torch.zeros(4, dtype=torch.int32, device=anchor.device)
+                params.append(tensors[key].data_ptr())
             elif p["kind"] == "tmap":
                 t = tensors[p["buffer"]]
                 params.append(driver.TensorMap(t.data_ptr() + p.get("offset_bytes", 0), p["dtype"], p["dims"], p["strides_bytes"],
@@ -180,14 +190,29 @@ class Problem:
             self.tensors[n].zero_()
         driver.launch(self.launches, self.stream)
         torch.cuda.synchronize(self.device)
+        self.check_status()
         return self.outputs()
+
+    def check_status(self) -> None:
+        """Raise if a kernel's bounded wait gave up (its status word is non-zero)."""
+        for tensors in [self.tensors] + list(getattr(self, "copies", [])):
+            for name, t in tensors.items():
+                if name.endswith(".status"):
+                    word = t.cpu().tolist()
+                    if word[0]:
+                        where = {1: "shared-memory stage never filled", 2: "shared-memory stage never released",
+                                 3: "accumulator never completed", 4: "accumulator never drained"}.get(word[0], "wait")
+                        raise driver.EmbError(-3, f"{name[:-7]}: a bounded wait ran out ({where}; code {word[0]}, "
+                                                  f"CTA {word[1]}, step {word[2]})")
 
     def outputs(self) -> dict:
         names = [a["name"] for k in self.meta["kernels"] for a in k["args"] if a.get("output")]
         return {n: to_numpy(self.tensors[n], self.dtypes[n]) for n in names}
 
     def time_us(self, warmup: int = 3, iters: int = 20, flush=None) -> list:
-        return driver.time_chain(self.launches, self.stream, warmup, iters, flush)
+        out = driver.time_chain(self.launches, self.stream, warmup, iters, flush)
+        self.check_status()
+        return out
 
     def rotate(self, min_bytes: int = 512 << 20, max_sets: int = 16) -> int:
         """Bind further copies of every tensor until the sets together hold ``min_bytes``:
@@ -203,7 +228,9 @@ class Problem:
 
     def time_rotating_us(self, warmup: int = 3, iters: int = 20, only=None, batch: int = 1) -> list:
         sets = self.sets if only is None else [[s[only]] for s in self.sets]
-        return driver.time_rotating(sets, self.stream, warmup, iters, batch)
+        out = driver.time_rotating(sets, self.stream, warmup, iters, batch)
+        self.check_status()
+        return out
 
     def launch_count(self) -> int:
         return len(self.launches)
@@ -229,8 +256,20 @@ def run_source(src, arrays: dict, mode: str = "optimized", device: int = 0) -> d
     fn = driver.Module(cubin).function(src.name)
     tensors = {n: to_torch(a, src.buffers[n].dtype, dev) for n, a in arrays.items()}
     li = kernel.launch
-    params = [tensors[p["name"]].data_ptr() for p in li["params"]]
+    params, status = [], None
+    for p in li["params"]:
+        if p["kind"] == "buffer":
+            params.append(tensors[p["name"]].data_ptr())
+        elif p["kind"] == "status":
+            status = torch.zeros(4, dtype=torch.int32, device=dev)
+            params.append(status.data_ptr())
+        else:
+            t = tensors[p["buffer"]]
+            params.append(driver.TensorMap(t.data_ptr() + p.get("offset_bytes", 0), p["dtype"], p["dims"], p["strides_bytes"],
+                                           p["box"], p.get("swizzle", "128B")))
     launch = driver.Launch(fn, li["grid"], li["block"], li["cluster"], li["smem_bytes"], params)
     driver.launch([launch], torch.cuda.current_stream(dev).cuda_stream)
     torch.cuda.synchronize(dev)
+    if status is not None and int(status[0]):
+        raise driver.EmbError(-3, f"{src.name}: a bounded wait ran out (status {status.cpu().tolist()})")
     return {n: to_numpy(tensors[n], src.buffers[n].dtype) for n in src.written}

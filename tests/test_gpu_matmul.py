@@ -1,0 +1,73 @@
+"""GPU parity of the tensor-core matmul template (tcgen05 + TMA + TMEM) against the oracle."""
+
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from emmy_ptx import problems, runner
+from helpers import margin, oracle_problem
+
+pytestmark = pytest.mark.gpu
+RTOL = 2e-3  # the stated tolerance for f16 / bf16 results
+ULP = {"f16": 2.0 ** -10, "bf16": 2.0 ** -8}  # one unit in the last place of the output format, relative
+
+
+def check(got, want, dtype="f16"):
+    """Both sides round an f32 sum once to the output format, so they may land on neighbouring
+    values: the tolerance is the stated 2e-3 plus one unit in the last place of that format (for
+    bf16 that unit, 2^-8, is itself larger than 2e-3). Near zero the scale is the RMS of the output."""
+    want64 = want.astype(np.float64)
+    rtol = RTOL + ULP[dtype]
+    atol = rtol * float(np.sqrt(np.mean(want64 ** 2)))
+    assert margin(got.astype(np.float64), want64, rtol, atol) <= 1
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 320), (384, 256, 1024), (200, 264, 72), (64, 128, 128)])
+def test_matmul_small_against_the_oracle(tmp_path, m, n, k, dtype):
+    block = 64 if (m * n) % 256 else 256
+    p = problems.matmul_f16(m=m, n=n, k=k, block=block, dtype=dtype, ident="t")
+    prob = runner.Problem(problems.write(p, tmp_path), "optimized")
+    assert prob.kernels[0].launch_info["family"] == "tensorcore"
+    got = prob.run()["matmul"]
+    want = oracle_problem(p, prob.host)["matmul"]
+    check(got, want, dtype)
+
+
+def test_matmul_strict_and_plain_keep_the_ir_order(tmp_path):
+    """--strict refuses the template (another summation order) and is bit-exact through the statement lowering."""
+    from helpers import same_bits
+    p = problems.matmul_f16(m=128, n=256, k=64, block=256, ident="t")
+    folder = problems.write(p, tmp_path)
+    want = None
+    for mode in ("strict", "plain"):
+        prob = runner.Problem(folder, mode)
+        assert prob.kernels[0].launch_info["family"] == "statements"
+        got = prob.run()["matmul"]
+        want = oracle_problem(p, prob.host)["matmul"] if want is None else want
+        if mode == "strict":
+            assert same_bits(got, want)
+        else:
+            check(got, want)
+
+
+def test_matmul_full_size_sampled_cells_and_properties():
+    import torch
+    folder = Path(runner.__file__).resolve().parent.parent / "problems" / "m_f16_8192"
+    prob = runner.Problem(folder, "optimized")
+    got = prob.run()["matmul"]
+    p = problems.matmul_f16()
+    grid = p["kernels"][0]["grid"]
+    rng = np.random.default_rng(7)
+    blocks = sorted({0, grid - 1, 31, 32, 8191 * 32 + 5, *rng.integers(0, grid, 19).tolist()})
+    want = oracle_problem(p, prob.host, blocks=blocks)["matmul"].reshape(-1)
+    cells = np.concatenate([np.arange(b * 256, (b + 1) * 256) for b in blocks])
+    check(got.reshape(-1)[cells], want[cells])
+    # the whole tensor against an f32 product on the same device (a cross-check, not the oracle)
+    a, b = prob.tensors["a"].float(), prob.tensors["b"].float()
+    ref = (a @ b.T).cpu().numpy()
+    check(got, ref)
+    # scaling an operand by a power of two scales the result exactly
+    doubled = runner.Problem(folder, "optimized", inputs={"a": prob.host["a"] * np.float16(2), "b": prob.host["b"]}).run()["matmul"]
+    assert np.array_equal(doubled, got * np.float16(2))
