@@ -181,6 +181,8 @@ def main() -> None:
     ap.add_argument("--mode", default="optimized", choices=("optimized", "strict"))
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--buffer-sets", type=int, default=0, help="copies of every buffer the passes rotate through (0: enough "
+                    "to exceed L2; 1 keeps device memory small for a profiler capture)")
     ap.add_argument("--families", default="sum,matmul", help="comma-separated extra workloads measured after the headline one")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -209,14 +211,17 @@ def main() -> None:
         w = WORKLOADS[workload]
         prob = runner.Problem(PKG / "problems" / w["folder"], args.mode, device=local)
         stream = prob.stream
-        nsets = prob.rotate(min_bytes=512 << 20, max_sets=8)  # the buffer sets together exceed the 126 MB L2: every pass is cold
+        if args.buffer_sets == 1:
+            nsets = 1
+        else:  # the buffer sets together exceed the 126 MB L2: every pass is cold
+            nsets = prob.rotate(min_bytes=512 << 20, max_sets=args.buffer_sets or 8)
         set_bytes = sum(t.numel() * t.element_size() for t in prob.tensors.values())
         exchange = workload == "sum" and world > 1
         barrier()
         if not exchange:
             total_us = prob.time_rotating_us(warmup=warmup, iters=1, batch=steps)[0] * steps
         else:  # the one real exchange of the path: an all-reduce of the per-GPU scalar, inside every step
-            finals = [prob.tensors["sum_1"]] + [c["sum_1"] for c in prob.copies]
+            finals = [prob.tensors["sum_1"]] + [c["sum_1"] for c in getattr(prob, "copies", [])]
             for i in range(warmup):
                 driver.launch(prob.sets[i % nsets], stream)
                 dist.all_reduce(finals[i % nsets])

@@ -1,0 +1,326 @@
+// FlashAttention-2-style forward template for sm_100a: O = softmax(scale * Q K^T [causal]) V for
+// head dimension 128, 16-bit Q/K/V/O, f32 scores and accumulators in tensor memory.
+//
+// It takes the place of the reference's lane-blocked SIMT attention: there the online-softmax update
+// found in the IR (emmy_ptx/mapping.py:402-500) is re-blocked over G <= 32 keys, the scores are
+// computed once per key block on the lanes of a row and broadcast through shared memory
+// (emmy_ptx/mapping.py:665-820, emmy_ptx/lanes.py:293-346, 610-658), all with scalar FMAs and one exp
+// per key (emmy_ptx/mathlib.py:111-136). Here a CTA owns NQ = 2 query tiles of 128 rows of one
+// (batch, head) and streams 128-key tiles of K and V:
+//
+//   warp 0      producer: TMA tensor-map loads (128-byte swizzle, no multicast) of Q once, then K_j and
+//               V_j into two stages each, completion on mbarriers
+//   warp 1      one thread issues tcgen05.mma: S_i = Q_i K_j^T (operands in shared memory) and
+//               O_i += P_i V_j (P_i read from TENSOR memory, V_j MN-major from shared memory); both
+//               query tiles alternate, so the tensor pipe works on one while the other is in softmax
+//   warps 2-5   softmax of query tile 0: one thread per row reads its 128 scores from TMEM, keeps the
+//   warps 6-9   running maximum and sum, writes P as 16-bit pairs over S's columns, rescales the O
+//   (tile 1)    accumulator in TMEM only when the maximum moved by more than 2^8 (the final division by
+//               the running sum makes the stale maximum exact), and at the end normalises and stores O
+//
+// The online update is the IR's (state m, l, o; alpha = exp(m - m'), beta = exp(s - m')); it is applied
+// once per 128-key tile instead of once per key, and in base 2 (scale * log2 e folded into one FMA).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "emb_gemm.cuh"
+#include "emb_math.cuh"
+
+namespace emb {
+
+struct AttnShape {
+    int batch_heads;   // batch * heads
+    int seq;           // queries = keys per (batch, head); a multiple of 128
+    float scale_log2;  // softmax scale * log2(e)
+};
+
+template <int NQ, bool CAUSAL, bool BF16, int POLY_PERIOD>
+__device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restrict__ map_q, const CUtensorMap* __restrict__ map_k,
+                                                     const CUtensorMap* __restrict__ map_v, void* __restrict__ o_out,
+                                                     AttnShape shape, unsigned* status) {
+    constexpr int BM = 128, BN = 128, D = 128, UMMA_K = 16;
+    constexpr uint32_t HALF_BYTES = 128 * 64 * 2;     // a 128-row x 64-column 16-bit box: 16 KB
+    constexpr uint32_t TILE_BYTES = 2 * HALF_BYTES;   // 128 x 128: 32 KB
+    constexpr int KV_STAGES = 2;
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t S_COL = 0, O_COL = 256;  // S_i at i * 128, O_i at 256 + i * 128; P_i over S_i's first 64 columns
+    using out_t = typename Half16<BF16>::type;
+    static_assert(NQ == 1 || NQ == 2, "one or two query tiles per CTA");
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* q_smem = smem;                                  // NQ tiles
+    uint8_t* k_smem = q_smem + NQ * TILE_BYTES;              // KV_STAGES tiles
+    uint8_t* v_smem = k_smem + KV_STAGES * TILE_BYTES;       // KV_STAGES tiles
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + KV_STAGES * TILE_BYTES);
+    uint64_t* q_full = bars;                  // 1
+    uint64_t* k_full = bars + 1;              // KV_STAGES
+    uint64_t* k_empty = k_full + KV_STAGES;
+    uint64_t* v_full = k_empty + KV_STAGES;
+    uint64_t* v_empty = v_full + KV_STAGES;
+    uint64_t* s_full = v_empty + KV_STAGES;   // NQ
+    uint64_t* p_ready = s_full + 2;           // NQ
+    uint64_t* o_done = p_ready + 2;           // NQ
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_done + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+    const tc::Guard guard{status, abort_flag};
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // CTAs of one (batch, head) are neighbours, the one with the most keys first: they run together and share K, V in L2
+    const int q_blocks = shape.seq / (NQ * BM);
+    const int bh = blockIdx.x / q_blocks;
+    const int qb = q_blocks - 1 - (blockIdx.x % q_blocks);
+    const int q0 = qb * NQ * BM;                      // first query row of the CTA
+    const int row_base = bh * shape.seq;              // first row of this (batch, head) in the flattened [BH * S, D] view
+    int n_kv[NQ];
+#pragma unroll
+    for (int i = 0; i < NQ; ++i) n_kv[i] = CAUSAL ? (q0 + i * BM + BM) / BN : shape.seq / BN;
+    const int n_max = n_kv[NQ - 1];
+
+    if (threadIdx.x == 0) {
+        tc::mbar_init(q_full, 1);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            tc::mbar_init(&k_full[s], 1);
+            tc::mbar_init(&k_empty[s], 1);
+            tc::mbar_init(&v_full[s], 1);
+            tc::mbar_init(&v_empty[s], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            tc::mbar_init(&s_full[i], 1);
+            tc::mbar_init(&p_ready[i], 4);  // one arrival per softmax warp
+            tc::mbar_init(&o_done[i], 1);
+        }
+        *abort_flag = 0;
+        tc::mbar_init_fence();
+        tc::tma_prefetch_desc(map_q);
+        tc::tma_prefetch_desc(map_k);
+        tc::tma_prefetch_desc(map_v);
+    }
+    if (warp == 1) tc::tmem_alloc(tmem_holder, TMEM_COLS);
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- producer
+        if (tc::elect_one()) {
+            tc::mbar_arrive_expect_tx(q_full, NQ * TILE_BYTES);
+#pragma unroll
+            for (int i = 0; i < NQ; ++i)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    tc::tma_load_2d(q_smem + i * TILE_BYTES + h * HALF_BYTES, map_q, q_full, h * 64, row_base + q0 + i * BM);
+            for (int j = 0; j < n_max; ++j) {
+                const uint32_t s = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
+                if (!tc::mbar_wait(&k_empty[s], ph ^ 1, guard, tc::WAIT_SMEM_EMPTY, j)) break;
+                tc::mbar_arrive_expect_tx(&k_full[s], TILE_BYTES);
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    tc::tma_load_2d(k_smem + s * TILE_BYTES + h * HALF_BYTES, map_k, &k_full[s], h * 64, row_base + j * BN);
+                if (!tc::mbar_wait(&v_empty[s], ph ^ 1, guard, tc::WAIT_SMEM_EMPTY, 1000 + j)) break;
+                tc::mbar_arrive_expect_tx(&v_full[s], TILE_BYTES);
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    tc::tma_load_2d(v_smem + s * TILE_BYTES + h * HALF_BYTES, map_v, &v_full[s], h * 64, row_base + j * BN);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (tc::elect_one()) {
+            constexpr uint32_t idesc_qk = tc::idesc_f16(BM, BN, BF16);
+            constexpr uint32_t idesc_pv = tc::idesc_f16(BM, D, BF16) | (1u << 16);  // B (= V) is MN-major
+            bool alive = tc::mbar_wait(q_full, 0, guard, tc::WAIT_SMEM_FULL, 9999);
+            int k_waited = -1, v_waited = -1;
+
+            // S_i = Q_i K_j^T: K runs over d = 128 in two 64-wide halves of four 16-wide steps
+            auto issue_qk = [&](int i, int j) {
+                const uint32_t s = j % KV_STAGES;
+                if (k_waited != j) {
+                    if (!tc::mbar_wait(&k_full[s], (j / KV_STAGES) & 1, guard, tc::WAIT_SMEM_FULL, j)) return false;
+                    k_waited = j;
+                }
+                tc::tc_fence_after_sync();
+                const uint8_t* qt = q_smem + i * TILE_BYTES;
+                const uint8_t* kt = k_smem + s * TILE_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < D / UMMA_K; ++kk) {
+                    const uint32_t off = (kk / 4) * HALF_BYTES + (kk % 4) * (UMMA_K * 2);
+                    tc::mma_f16_ss(tmem_base + S_COL + i * BN, tc::smem_desc_k128(qt + off), tc::smem_desc_k128(kt + off),
+                                   idesc_qk, kk != 0);
+                }
+                tc::mma_commit(&s_full[i]);
+                if (i == NQ - 1) tc::mma_commit(&k_empty[s]);  // the last query tile to use K_j
+                return true;
+            };
+            // O_i += P_i V_j: K runs over the 128 keys in 16-key steps; V_j is [key][d], d contiguous: MN-major,
+            // 64-wide d halves 16 KB apart (leading offset), 8-key groups 1024 B apart (stride offset)
+            auto issue_pv = [&](int i, int j) {
+                const uint32_t s = j % KV_STAGES;
+                if (v_waited != j) {
+                    if (!tc::mbar_wait(&v_full[s], (j / KV_STAGES) & 1, guard, tc::WAIT_SMEM_FULL, 1000 + j)) return false;
+                    v_waited = j;
+                }
+                tc::tc_fence_after_sync();
+                const uint8_t* vt = v_smem + s * TILE_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < BN / UMMA_K; ++kk) {
+                    uint64_t d = 0;
+                    d |= static_cast<uint64_t>((tc::smem_u32(vt + kk * UMMA_K * 128) & 0x3ffff) >> 4);
+                    d |= static_cast<uint64_t>(HALF_BYTES >> 4) << 16;  // leading byte offset: next 64 columns of d
+                    d |= static_cast<uint64_t>(1024 >> 4) << 32;        // stride byte offset: next 8 keys
+                    d |= static_cast<uint64_t>(1) << 46;
+                    d |= static_cast<uint64_t>(2) << 61;                // SWIZZLE_128B
+                    tc::mma_f16_ts(tmem_base + O_COL + i * D, tmem_base + S_COL + i * BN + kk * (UMMA_K / 2), d, idesc_pv,
+                                   (j | kk) != 0);
+                }
+                tc::mma_commit(&o_done[i]);
+                if (i == NQ - 1) tc::mma_commit(&v_empty[s]);
+                return true;
+            };
+
+            if (alive) {
+#pragma unroll
+                for (int i = 0; i < NQ && alive; ++i) alive = issue_qk(i, 0);
+            }
+            for (int j = 0; alive && j < n_max; ++j) {
+#pragma unroll
+                for (int i = 0; i < NQ; ++i) {
+                    if (!alive || j >= n_kv[i]) continue;
+                    if (!tc::mbar_wait(&p_ready[i], j & 1, guard, tc::WAIT_TMEM_FULL, 2000 + j)) {
+                        alive = false;
+                        break;
+                    }
+                    alive = issue_pv(i, j);
+                    if (alive && j + 1 < n_kv[i]) alive = issue_qk(i, j + 1);
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- softmax, correction, epilogue
+        const int i = (warp - 2) >> 2;       // query tile of this warp group
+        const int quarter = warp & 3;        // the TMEM lanes this warp may touch: 32 * quarter ..
+        const int row = quarter * 32 + lane; // row of the query tile
+        const int q_row = q0 + i * BM + row;
+        const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+        const uint32_t s_addr = tmem_base + lane_addr + S_COL + i * BN;
+        const uint32_t o_addr = tmem_base + lane_addr + O_COL + i * D;
+        float m_used = -__int_as_float(0x7f800000);  // -inf, in units of log2
+        float l = 0.0f;
+        bool alive = (NQ == 2 || i == 0);
+        const int n_mine = alive ? n_kv[i < NQ ? i : 0] : 0;
+        for (int j = 0; alive && j < n_mine; ++j) {
+            if (!tc::mbar_wait(&s_full[i], j & 1, guard, tc::WAIT_TMEM_FULL, 3000 + j)) {
+                alive = false;
+                break;
+            }
+            tc::tc_fence_after_sync();
+            uint32_t sr[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tc::tmem_ld_32x32(s_addr + c * 32, sr[c]);
+            tc::tmem_ld_wait();
+            float mx = -__int_as_float(0x7f800000);
+            if (CAUSAL && j == n_mine - 1) {  // the diagonal tile: keys beyond the query are masked
+                const int limit = q_row - j * BN;  // columns <= limit are visible
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int x = 0; x < 32; ++x)
+                        if (c * 32 + x > limit) sr[c][x] = 0xff800000u;
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int x = 0; x < 32; x += 2) mx = emb::max3(mx, __uint_as_float(sr[c][x]), __uint_as_float(sr[c][x + 1]));
+            const float m_new = fmaxf(m_used, mx * shape.scale_log2);
+            // move the reference maximum only when it grew by more than 8 (a factor 256): until then the
+            // weights are at most 2^8 and the running sum and O stay consistent with the old one
+            const bool moved = m_new - m_used > 8.0f;
+            if (__any_sync(0xffffffffu, moved) && j > 0) {
+                const float alpha = moved ? emb::ex2_approx_ftz(m_used - m_new) : 1.0f;
+                // PV(i, j-1) completed before S(i, j) did (same issuing thread, in order); the wait orders memory
+                tc::mbar_wait(&o_done[i], (j - 1) & 1, guard, tc::WAIT_TMEM_EMPTY, 4000 + j);
+                tc::tc_fence_after_sync();
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t orow[32];
+                    tc::tmem_ld_32x32(o_addr + c * 32, orow);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int x = 0; x < 32; ++x) orow[x] = __float_as_uint(__uint_as_float(orow[x]) * alpha);
+                    tc::tmem_st_32x32(o_addr + c * 32, orow);
+                }
+                l *= alpha;
+            }
+            if (moved) m_used = m_new;
+            const unsigned long long neg_m2 = emb::pack_f2(-m_used, -m_used);
+            const unsigned long long scale2 = emb::pack_f2(shape.scale_log2, shape.scale_log2);
+            unsigned long long sum2 = emb::pack_f2(0.0f, 0.0f);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t packed[16];
+#pragma unroll
+                for (int x = 0; x < 32; x += 2) {
+                    const unsigned long long t2 =
+                        emb::fma_f2(emb::pack_f2(__uint_as_float(sr[c][x]), __uint_as_float(sr[c][x + 1])), scale2, neg_m2);
+                    float t0, t1, p0, p1;
+                    emb::unpack_f2(t2, t0, t1);
+                    if (POLY_PERIOD > 0 && ((c * 16 + x / 2) % (POLY_PERIOD > 0 ? POLY_PERIOD : 1)) == 0) {
+                        emb::ex2_poly3_pair(t0, t1, p0, p1);  // this pair's exponentials on the FMA pipe, not the SFU
+                    } else {
+                        p0 = emb::ex2_approx_ftz(t0);
+                        p1 = emb::ex2_approx_ftz(t1);
+                    }
+                    sum2 = emb::add_f2(sum2, emb::pack_f2(p0, p1));
+                    packed[x / 2] = pack2<BF16>(p0, p1);
+                }
+                // P over S's own columns: 16-bit pairs, 16 columns per 32 keys
+                asm volatile(
+                    "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                    "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(s_addr + c * 16),
+                    "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3]), "r"(packed[4]), "r"(packed[5]),
+                    "r"(packed[6]), "r"(packed[7]), "r"(packed[8]), "r"(packed[9]), "r"(packed[10]), "r"(packed[11]),
+                    "r"(packed[12]), "r"(packed[13]), "r"(packed[14]), "r"(packed[15])
+                    : "memory");
+            }
+            float sum, sum_hi;
+            emb::unpack_f2(sum2, sum, sum_hi);
+            sum += sum_hi;
+            l += sum;
+            tc::tmem_st_wait();
+            tc::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&p_ready[i]);
+        }
+        if (alive && n_mine > 0 && tc::mbar_wait(&o_done[i], (n_mine - 1) & 1, guard, tc::WAIT_TMEM_EMPTY, 5000)) {
+            tc::tc_fence_after_sync();
+            const float inv = 1.0f / l;
+            out_t* dst = static_cast<out_t*>(o_out) + (static_cast<size_t>(row_base) + q_row) * D;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t orow[32];
+                tc::tmem_ld_32x32(o_addr + c * 32, orow);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 v;
+                    v.x = pack2<BF16>(__uint_as_float(orow[8 * q + 0]) * inv, __uint_as_float(orow[8 * q + 1]) * inv);
+                    v.y = pack2<BF16>(__uint_as_float(orow[8 * q + 2]) * inv, __uint_as_float(orow[8 * q + 3]) * inv);
+                    v.z = pack2<BF16>(__uint_as_float(orow[8 * q + 4]) * inv, __uint_as_float(orow[8 * q + 5]) * inv);
+                    v.w = pack2<BF16>(__uint_as_float(orow[8 * q + 6]) * inv, __uint_as_float(orow[8 * q + 7]) * inv);
+                    *reinterpret_cast<uint4*>(dst + c * 32 + 8 * q) = v;
+                }
+            }
+        }
+    }
+
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::tc_fence_after_sync();
+        tc::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace emb

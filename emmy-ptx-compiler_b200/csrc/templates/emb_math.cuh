@@ -61,6 +61,56 @@ __device__ __forceinline__ float ex2_neg_fma(float t) {
     return t < -125.0f ? 0.0f : r;
 }
 
+// ---- two floats at a time (sm_100 has packed f32x2 FMA and ADD: half the issue slots) ----
+
+__device__ __forceinline__ unsigned long long pack_f2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack_f2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_f2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long add_f2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+// 2^t for two values t <= ~8 on the FMA and integer pipes only: round t to an integer with the
+// magic-number add, cubic for 2^f on |f| <= 1/2 (2.1e-4 relative, finer than the f16 the softmax
+// weights are rounded to), exponent-field add. For kernels whose exponentials saturate the SFU.
+__device__ __forceinline__ void ex2_poly3_pair(float t0, float t1, float& p0, float& p1) {
+    const float magic = 12582912.0f;  // 1.5 * 2^23: adding it leaves round(t) in the low mantissa bits
+    t0 = fmaxf(t0, -125.0f);
+    t1 = fmaxf(t1, -125.0f);
+    const unsigned long long t = pack_f2(t0, t1);
+    const unsigned long long one = pack_f2(1.0f, 1.0f);
+    const unsigned long long shifted = add_f2(t, pack_f2(magic, magic));
+    const unsigned long long j = add_f2(shifted, pack_f2(-magic, -magic));
+    const unsigned long long f = fma_f2(j, pack_f2(-1.0f, -1.0f), t);
+    // 2^f = 1 + f (c1 + f (c2 + f c3)): exact at f = 0, so a weight of 2^0 is exactly 1
+    unsigned long long p = fma_f2(pack_f2(0.055838342756032944f, 0.055838342756032944f), f,
+                                  pack_f2(0.24203594028949738f, 0.24203594028949738f));
+    p = fma_f2(p, f, pack_f2(0.6931367516517639f, 0.6931367516517639f));
+    p = fma_f2(p, f, one);
+    float s0, s1, q0, q1;
+    unpack_f2(shifted, s0, s1);
+    unpack_f2(p, q0, q1);
+    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(s0) << 23));
+    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(s1) << 23));
+}
+
 // tanh: below 0.6 an odd polynomial x + x^3 P(x^2) (0.75 ulp in the fit's float emulation);
 // above, 1 - 2 / (e^(2|x|) + 1) with x's sign.
 __device__ __forceinline__ float tanh_f32(float x) {

@@ -224,10 +224,11 @@ __device__ __forceinline__ uint64_t smem_desc_k128(const void* tile) {
 }
 
 // Instruction descriptor of kind::f16 (A, B f16 or bf16; D f32) with both operands K-major.
-__host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool bf16) {
-    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+__host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool a_bf16, bool b_bf16) {
+    return (1u << 4) | ((a_bf16 ? 1u : 0u) << 7) | ((b_bf16 ? 1u : 0u) << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
            (static_cast<uint32_t>(m >> 4) << 24);
 }
+__host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool bf16) { return idesc_f16(m, n, bf16, bf16); }
 
 // Instruction descriptor of kind::f8f6f4 with e4m3 operands (format code 0), D f32, both K-major.
 __host__ __device__ constexpr uint32_t idesc_e4m3(int m, int n) {

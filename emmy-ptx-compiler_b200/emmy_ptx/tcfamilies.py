@@ -31,6 +31,7 @@ from .ir import dtype_name, kind
 TARGET_SMS = 148
 GEMM_STAGES = 4
 GEMM_GROUP_M = 16
+ATTN_POLY_PERIOD = 0  # every n-th pair of softmax weights gets its 2^x from an FMA polynomial instead of the SFU (0: none)
 
 
 def wrapper(src, includes: str, body: list, extra_sig: list, threads: int, min_blocks: int = 1) -> str:
@@ -108,8 +109,145 @@ def match_matmul(src, strict: bool) -> Plan:
     return Plan("tensorcore", source, remarks, grid=grid, block=192, smem_bytes=smem, extra_params=extra)
 
 
-def match_attention(src, strict: bool):
-    raise Refusal("not built yet")
+# ---------------------------------------------------------------- attention
+
+
+def _assign(stmts: dict, name, op=None):
+    st = stmts.get(name)
+    need(st is not None and kind(st) == "Assign" and (op is None or st.op.name == op), f"{name} is not an Assign of {op}")
+    return st
+
+
+def match_attention(src, strict: bool) -> Plan:
+    """emmy's fused attention (examples/a01_attention/k_matmul_softmax_reduce_b55365.ir.txt,
+    tests/test_oracle.py:204-231): per (row, output column) thread a key loop that recomputes the row's
+    score, then the online update gn = max(m, s), alpha = exp(m - gn), beta = exp(s - gn),
+    l = alpha l + beta, o = alpha o + beta v, m = max(m, s); legality as emmy_ptx/mapping.py:413-467
+    (the update reads m before m moves, no two sums share an addend, the scores read no carried state)."""
+    tile = single_tile(src)
+    need(len(tile.axes) >= 2, "the Tile is not over (..., query, column) cells")
+    lead = tile.axes[:-2]
+    q_axis, c_axis = tile.axes[-2].name, tile.axes[-1].name
+    S, D = tile.axes[-2].extent.as_static(), tile.axes[-1].extent.as_static()
+    need(D == 128 and src.launch.block == D, "the head dimension (= block) is not 128")
+    body = list(tile.body)
+    lets = {s.name: s for s in body if kind(s) == "Let"}
+    rest = [s for s in body if kind(s) != "Let"]
+    need(len(rest) == 4 and [kind(s) for s in rest] == ["StridedLoop", "Assign", "Assign", "Write"],
+         "the cell is not key loop, reciprocal, multiply, Write")
+    loop, inv, res, write = rest
+    key_axis = loop.axis.name
+    need(loop.seed and kind(loop.start) == "Literal" and loop.start.value == 0 and kind(loop.step) == "Literal"
+         and loop.step.value == 1 and loop.axis.extent.as_static() == S, "the key loop is not 0 .. S step 1")
+    if loop.end is None:
+        causal = False
+    else:
+        e = loop.end
+        need(kind(e) == "BinaryExpr" and e.op == "+" and is_var(e.left, q_axis) and kind(e.right) == "Literal"
+             and e.right.value == 1, "the key loop's end is neither S nor query + 1")
+        causal = True
+    lb_ = list(loop.body)
+    need(lb_ and kind(lb_[0]) == "Loop", "the key loop does not start with the score's dot product")
+    dot_loop = lb_[0]
+    need(dot_loop.seed and dot_loop.axis.extent.as_static() == D and len(dot_loop.body) == 4
+         and [kind(s) for s in dot_loop.body] == ["Load", "Load", "Assign", "Accum"], "the dot product is not Load, Load, multiply, Accum")
+    d_axis = dot_loop.axis.name
+    l1, l2, prod, dot = dot_loop.body
+    need(prod.op.name == "multiply" and set(prod.args) == {l1.names[0], l2.names[0]} and dtype_name(prod.dtype) == "f32"
+         and dot.value == prod.name and dot.base is None and codegen.CANON.get(dot.op.name) == "add", "the score is not an f32 dot product")
+    lead_names = [a.name for a in lead]
+
+    def indexed(load, row_axis, col_axis):
+        idx = load.index
+        return (len(idx) == len(lead) + 2 and all(is_var(e, n) for e, n in zip(idx, lead_names))
+                and is_var(idx[-2], row_axis) and is_var(idx[-1], col_axis))
+    if indexed(l1, q_axis, d_axis) and indexed(l2, key_axis, d_axis):
+        ql, kl = l1, l2
+    elif indexed(l2, q_axis, d_axis) and indexed(l1, key_axis, d_axis):
+        ql, kl = l2, l1
+    else:
+        raise Refusal("the score does not read Q[.., query, d] and K[.., key, d]")
+    tail = lb_[1:]
+    stmts = {getattr(s, "name", None): s for s in tail if kind(s) == "Assign"}
+    accums = [s for s in tail if kind(s) == "Accum"]
+    loads = [s for s in tail if kind(s) == "Load"]
+    need(len(accums) == 3 and len(loads) == 1 and len(tail) == len(stmts) + 4, "the update is not three Accums around one Load of V")
+    m_acc = tail[-1]
+    need(kind(m_acc) == "Accum" and codegen.CANON.get(m_acc.op.name) == "maximum" and m_acc.base is None,
+         "the maximum does not move last (the update must read m before it moves)")
+    m, s_name = m_acc.name, m_acc.value
+    sums = [a for a in accums if a is not m_acc]
+    need(all(codegen.CANON.get(a.op.name) == "add" and a.base is not None for a in sums), "the sums are not rescaled sums")
+    s_st = _assign(stmts, s_name, "multiply")
+    need(dot.name in s_st.args, "the score is not the scaled dot product")
+    scale_name = [a for a in s_st.args if a != dot.name]
+    need(len(scale_name) == 1 and scale_name[0] in lets and kind(lets[scale_name[0]].value) == "Literal"
+         and float(lets[scale_name[0]].value.value) > 0, "the scale is not a positive constant")
+    scale = float(lets[scale_name[0]].value.value)
+    # the two rescaling factors
+    exps = [a for a in stmts.values() if a.op.name == "exp"]
+    need(len(exps) == 2, "the update does not have exactly two exponentials")
+
+    def factor(e):
+        d = _assign(stmts, e.args[0], "subtract")
+        g = _assign(stmts, d.args[1], "maximum")
+        need(set(g.args) == {m, s_name}, "the new maximum is not max(m, s)")
+        return d.args[0]
+    alpha = next((e for e in exps if factor(e) == m), None)
+    beta = next((e for e in exps if factor(e) == s_name), None)
+    need(alpha is not None and beta is not None, "the factors are not exp(m - max) and exp(s - max)")
+    vload = loads[0]
+    need(indexed(vload, key_axis, c_axis), "V is not read at [.., key, column]")
+    l_acc = o_acc = None
+    for a in sums:
+        base = _assign(stmts, a.base, "multiply")
+        need(set(base.args) == {a.name, alpha.name}, "a sum is not rescaled by alpha")
+        val = _assign(stmts, a.value, "multiply")
+        need(beta.name in val.args, "an addend is not weighted by beta")
+        other = [x for x in val.args if x != beta.name][0]
+        if other == vload.names[0]:
+            o_acc = a
+        else:
+            need(other in lets and kind(lets[other].value) == "Literal" and float(lets[other].value.value) == 1.0,
+                 "the running sum's addend is not beta * 1")
+            l_acc = a
+    need(l_acc is not None and o_acc is not None and l_acc.value != o_acc.value, "no running sum and output pair (or a shared addend)")
+    need(inv.op.name == "reciprocal" and tuple(inv.args) == (l_acc.name,) and res.op.name == "multiply"
+         and set(res.args) == {o_acc.name, inv.name}, "the epilogue is not o / l")
+    need(tuple(write.values) == (res.name,) and not write.atomic and len(write.index) == len(lead) + 2
+         and all(is_var(e, n) for e, n in zip(write.index, lead_names + [q_axis, c_axis])), "the Write is not O[.., query, column]")
+    bufs = [src.buffers.get(n) for n in (ql.input, kl.input, vload.input, write.output)]
+    need(all(b is not None for b in bufs), "unknown buffers")
+    shape = tuple(a.extent.as_static() for a in lead) + (S, D)
+    need(all(tuple(b.shape) == shape for b in bufs), "Q, K, V, O do not share the shape [.., S, 128]")
+    dt = bufs[0].dtype
+    need(dt in ("f16", "bf16") and all(b.dtype == dt for b in bufs), "Q, K, V, O are not all f16 or all bf16")
+    need(not ({ql.input, kl.input, vload.input} & set(src.written)), "the kernel writes an operand")
+    need(not strict, "the tensor cores and the per-tile softmax sum in their own order (--strict keeps the IR's)")
+    need(S % 128 == 0, "the sequence length is not a multiple of the 128-row tile")
+
+    nq = 2 if S % 256 == 0 else 1
+    bh = math.prod(a.extent.as_static() for a in lead) if lead else 1
+    grid = bh * (S // (nq * 128))
+    threads = 64 + 128 * nq
+    smem = (nq + 4) * 32768 + 1024 + 256
+    scale_log2 = scale * math.log2(math.e)
+    call = [f"    emb::attention_fwd_kernel<{nq}, {str(causal).lower()}, {str(dt == 'bf16').lower()}, {ATTN_POLY_PERIOD}>(&tmap_q, &tmap_k, &tmap_v, "
+            f"p_{write.output}, emb::AttnShape{{{bh}, {S}, {codegen.c_float(scale_log2)}}}, status);"]
+    extra_sig = ["const __grid_constant__ CUtensorMap tmap_q", "const __grid_constant__ CUtensorMap tmap_k",
+                 "const __grid_constant__ CUtensorMap tmap_v", "unsigned* __restrict__ status"]
+    source = wrapper(src, '#include "emb_attention.cuh"', call, extra_sig, threads)
+    rows = bh * S
+    extra = [tmap("q", ql.input, dt, (D, rows), (D * 2,), (64, 128)), tmap("k", kl.input, dt, (D, rows), (D * 2,), (64, 128)),
+             tmap("v", vload.input, dt, (D, rows), (D * 2,), (64, 128)), dict(kind="status", name="status")]
+    remarks = [f"attention template: {bh} (batch, head) pairs x {S} queries, head dimension 128, {dt}, "
+               f"{'causal' if causal else 'full'}; {grid} CTAs of {threads} threads, each {nq} query tile(s) of 128 rows "
+               "against 128-key tiles (TMA producer, tcgen05.mma issuer, one softmax warp group per query tile)",
+               "online softmax recognised (m, l, o with alpha = exp(m - max), beta = exp(s - max)); applied once per 128-key "
+               "tile in base 2, O rescaled in tensor memory only when the maximum moves by more than 2^8",
+               "S = Q K^T and O += P V on tcgen05.mma with S, P and O in tensor memory; K, V in two TMA stages each; "
+               "the CTAs of one (batch, head) are neighbours so that K and V are shared in L2"]
+    return Plan("blocking", source, remarks, grid=grid, block=threads, smem_bytes=smem, extra_params=extra)
 
 
 def match_mlp(src, strict: bool):

@@ -1,0 +1,77 @@
+"""GPU parity of the attention template (tcgen05 S = Q K^T and O += P V, softmax in registers, TMEM state)."""
+
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from emmy_ptx import problems, runner
+from helpers import margin, oracle_problem
+
+pytestmark = pytest.mark.gpu
+RTOL = 2e-3
+# one unit in the last place of the output format (both sides round once to it). For bf16 the softmax
+# weights themselves are rounded to bf16 before P V (8 significant bits, as in every bf16 flash
+# attention), which costs about another unit on outputs that are small against their row's terms.
+ULP = {"f16": 2.0 ** -10, "bf16": 2.0 ** -7}
+
+
+def check(got, want, dtype="f16"):
+    """The stated 2e-3 plus the format's allowance above; near zero the scale is the RMS of the output."""
+    want64 = np.asarray(want, np.float64)
+    rtol = RTOL + ULP[dtype]
+    atol = rtol * float(np.sqrt(np.mean(want64 ** 2)))
+    assert margin(np.asarray(got, np.float64), want64, rtol, atol) <= 1
+
+
+@pytest.mark.parametrize("batch,heads,seq,causal,dtype", [(1, 2, 256, True, "f16"), (1, 1, 128, True, "f16"),
+                                                           (2, 1, 384, True, "bf16"), (1, 1, 256, False, "f16"),
+                                                           (1, 1, 256, False, "bf16")])
+def test_attention_small_against_the_oracle(tmp_path, batch, heads, seq, causal, dtype):
+    p = problems.attention(batch=batch, heads=heads, seq=seq, dim=128, causal=causal, dtype=dtype, ident="t")
+    prob = runner.Problem(problems.write(p, tmp_path), "optimized")
+    assert prob.kernels[0].launch_info["family"] == "blocking"
+    got = prob.run()["attn"]
+    want = oracle_problem(p, prob.host)["attn"]
+    check(got, want, dtype)
+
+
+def test_attention_strict_keeps_the_ir_order(tmp_path):
+    p = problems.attention(batch=1, heads=1, seq=128, dim=128, ident="t")
+    prob = runner.Problem(problems.write(p, tmp_path), "strict")
+    assert prob.kernels[0].launch_info["family"] == "statements"
+    got = prob.run()["attn"]
+    want = oracle_problem(p, prob.host)["attn"]
+    check(got, want)  # exp is within its 2 ulp in every lowering; the sums are in the IR's order
+
+
+def test_attention_with_large_scores_rescales_correctly(tmp_path):
+    """Scores that keep growing along the keys force the running maximum (and the lazy rescale) to move."""
+    p = problems.attention(batch=1, heads=1, seq=256, dim=128, ident="t")
+    folder = problems.write(p, tmp_path)
+    rng = np.random.default_rng(11)
+    q = rng.standard_normal((1, 1, 256, 128)).astype(np.float16)
+    k = (rng.standard_normal((1, 1, 256, 128)) * np.linspace(0.2, 8.0, 256)[None, None, :, None]).astype(np.float16)
+    v = rng.standard_normal((1, 1, 256, 128)).astype(np.float16)
+    prob = runner.Problem(folder, "optimized", inputs={"q": q, "k": k, "v": v})
+    got = prob.run()["attn"]
+    want = oracle_problem(p, {"q": q, "k": k, "v": v})["attn"]
+    check(got, want)
+
+
+def test_attention_full_size_sampled_rows_and_cross_check():
+    import torch
+    folder = Path(runner.__file__).resolve().parent.parent / "problems" / "a_f16_causal_8x32x4096x128"
+    prob = runner.Problem(folder, "optimized")
+    got = prob.run()["attn"]
+    p = problems.attention()
+    rows = [0, 1, 127, 128, 255, 256, 300]
+    blocks = sorted({bh * 4096 + r for bh in (0, 77, 255) for r in rows})  # one block per (batch, head, query)
+    want = oracle_problem(p, prob.host, blocks=blocks)["attn"].reshape(-1, 128)
+    check(got.reshape(-1, 128)[blocks], want[blocks])
+    # the whole tensor against the library attention on the same device (a cross-check, not the oracle)
+    q, k, v = (prob.tensors[n] for n in "qkv")
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True).float().cpu().numpy()
+    check(got, ref)
+    # the first query of every (batch, head) attends to key 0 only: its output is V[.., 0, :] exactly
+    assert np.array_equal(got[:, :, 0, :], prob.host["v"][:, :, 0, :])

@@ -68,6 +68,8 @@ def test_matmul_full_size_sampled_cells_and_properties():
     a, b = prob.tensors["a"].float(), prob.tensors["b"].float()
     ref = (a @ b.T).cpu().numpy()
     check(got, ref)
-    # scaling an operand by a power of two scales the result exactly
+    # scaling an operand by a power of two scales every result exactly (where the f16 result is a
+    # normal number: in the subnormal range the rounding step does not scale)
     doubled = runner.Problem(folder, "optimized", inputs={"a": prob.host["a"] * np.float16(2), "b": prob.host["b"]}).run()["matmul"]
-    assert np.array_equal(doubled, got * np.float16(2))
+    normal = np.abs(got) >= np.float16(2.0 ** -13)
+    assert normal.mean() > 0.9 and np.array_equal(doubled[normal], (got * np.float16(2))[normal])
