@@ -62,7 +62,8 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
     uint64_t* s_full = v_empty + KV_STAGES;   // NQ
     uint64_t* p_ready = s_full + 2;           // NQ
     uint64_t* o_done = p_ready + 2;           // NQ
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_done + 2);
+    uint64_t* p_half = o_done + 2;            // NQ: the first 64 keys of P are written
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(p_half + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
     const tc::Guard guard{status, abort_flag};
 
@@ -89,6 +90,7 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
         for (int i = 0; i < 2; ++i) {
             tc::mbar_init(&s_full[i], 1);
             tc::mbar_init(&p_ready[i], 4);  // one arrival per softmax warp
+            tc::mbar_init(&p_half[i], 4);
             tc::mbar_init(&o_done[i], 1);
         }
         *abort_flag = 0;
@@ -156,7 +158,7 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
             };
             // O_i += P_i V_j: K runs over the 128 keys in 16-key steps; V_j is [key][d], d contiguous: MN-major,
             // 64-wide d halves 16 KB apart (leading offset), 8-key groups 1024 B apart (stride offset)
-            auto issue_pv = [&](int i, int j) {
+            auto issue_pv = [&](int i, int j, int half) {
                 const uint32_t s = j % KV_STAGES;
                 if (v_waited != j) {
                     if (!tc::mbar_wait(&v_full[s], (j / KV_STAGES) & 1, guard, tc::WAIT_SMEM_FULL, 1000 + j)) return false;
@@ -165,7 +167,7 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
                 tc::tc_fence_after_sync();
                 const uint8_t* vt = v_smem + s * TILE_BYTES;
 #pragma unroll
-                for (int kk = 0; kk < BN / UMMA_K; ++kk) {
+                for (int kk = half * 4; kk < half * 4 + 4; ++kk) {
                     uint64_t d = 0;
                     d |= static_cast<uint64_t>((tc::smem_u32(vt + kk * UMMA_K * 128) & 0x3ffff) >> 4);
                     d |= static_cast<uint64_t>(HALF_BYTES >> 4) << 16;  // leading byte offset: next 64 columns of d
@@ -175,8 +177,10 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
                     tc::mma_f16_ts(tmem_base + O_COL + i * D, tmem_base + S_COL + i * BN + kk * (UMMA_K / 2), d, idesc_pv,
                                    (j | kk) != 0);
                 }
-                tc::mma_commit(&o_done[i]);
-                if (i == NQ - 1) tc::mma_commit(&v_empty[s]);
+                if (half == 1) {
+                    tc::mma_commit(&o_done[i]);
+                    if (i == NQ - 1) tc::mma_commit(&v_empty[s]);
+                }
                 return true;
             };
 
@@ -188,11 +192,16 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
 #pragma unroll
                 for (int i = 0; i < NQ; ++i) {
                     if (!alive || j >= n_kv[i]) continue;
-                    if (!tc::mbar_wait(&p_ready[i], j & 1, guard, tc::WAIT_TMEM_FULL, 2000 + j)) {
+                    if (!tc::mbar_wait(&p_half[i], j & 1, guard, tc::WAIT_TMEM_FULL, 2000 + j)) {
                         alive = false;
                         break;
                     }
-                    alive = issue_pv(i, j);
+                    alive = issue_pv(i, j, 0);
+                    if (!alive || !tc::mbar_wait(&p_ready[i], j & 1, guard, tc::WAIT_TMEM_FULL, 2500 + j)) {
+                        alive = false;
+                        break;
+                    }
+                    alive = issue_pv(i, j, 1);
                     if (alive && j + 1 < n_kv[i]) alive = issue_qk(i, j + 1);
                 }
             }
@@ -216,23 +225,32 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
                 break;
             }
             tc::tc_fence_after_sync();
-            uint32_t sr[4][32];
+            const bool diagonal = CAUSAL && j == n_mine - 1;  // keys beyond the query are masked
+            const int limit = q_row - j * BN;                 // on the diagonal tile columns <= limit are visible
+            uint32_t sr[2][32];                               // two chunks of 32 scores: one in use, one in flight
+            // pass 1: the row maximum (eight independent chains, the next chunk's TMEM load in flight)
+            float mx8[8];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tc::tmem_ld_32x32(s_addr + c * 32, sr[c]);
-            tc::tmem_ld_wait();
-            float mx = -__int_as_float(0x7f800000);
-            if (CAUSAL && j == n_mine - 1) {  // the diagonal tile: keys beyond the query are masked
-                const int limit = q_row - j * BN;  // columns <= limit are visible
+            for (int u = 0; u < 8; ++u) mx8[u] = -__int_as_float(0x7f800000);
+            tc::tmem_ld_32x32(s_addr, sr[0]);
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < 4; ++c) {
+                tc::tmem_ld_wait();
+                if (c + 1 < 4) tc::tmem_ld_32x32(s_addr + (c + 1) * 32, sr[(c + 1) & 1]);
+                uint32_t(&cur)[32] = sr[c & 1];
+                if (diagonal) {
 #pragma unroll
                     for (int x = 0; x < 32; ++x)
-                        if (c * 32 + x > limit) sr[c][x] = 0xff800000u;
+                        if (c * 32 + x > limit) cur[x] = 0xff800000u;
+                }
+#pragma unroll
+                for (int x = 0; x < 32; x += 4)
+                    mx8[(x / 4) & 7] = emb::max3(mx8[(x / 4) & 7], emb::max3(__uint_as_float(cur[x]), __uint_as_float(cur[x + 1]),
+                                                                             __uint_as_float(cur[x + 2])),
+                                                 __uint_as_float(cur[x + 3]));
             }
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-#pragma unroll
-                for (int x = 0; x < 32; x += 2) mx = emb::max3(mx, __uint_as_float(sr[c][x]), __uint_as_float(sr[c][x + 1]));
+            const float mx = fmaxf(emb::max3(mx8[0], mx8[1], mx8[2]), emb::max3(emb::max3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
+            tc::tmem_ld_32x32(s_addr, sr[0]);  // pass 2 starts: chunk 0 again, in flight during the bookkeeping
             const float m_new = fmaxf(m_used, mx * shape.scale_log2);
             // move the reference maximum only when it grew by more than 8 (a factor 256): until then the
             // weights are at most 2^8 and the running sum and O stay consistent with the old one
@@ -254,28 +272,37 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
                 l *= alpha;
             }
             if (moved) m_used = m_new;
+            // pass 2: weights 2^(s * scale - m), their sum, and P as 16-bit pairs over S's own columns
+            // (chunk c of P lands on columns 16c .. 16c+15, all of them scores already consumed)
             const unsigned long long neg_m2 = emb::pack_f2(-m_used, -m_used);
             const unsigned long long scale2 = emb::pack_f2(shape.scale_log2, shape.scale_log2);
-            unsigned long long sum2 = emb::pack_f2(0.0f, 0.0f);
+            unsigned long long sum2[2] = {emb::pack_f2(0.0f, 0.0f), emb::pack_f2(0.0f, 0.0f)};
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
+                tc::tmem_ld_wait();
+                if (c + 1 < 4) tc::tmem_ld_32x32(s_addr + (c + 1) * 32, sr[(c + 1) & 1]);
+                uint32_t(&cur)[32] = sr[c & 1];
+                if (diagonal) {
+#pragma unroll
+                    for (int x = 0; x < 32; ++x)
+                        if (c * 32 + x > limit) cur[x] = 0xff800000u;
+                }
                 uint32_t packed[16];
 #pragma unroll
                 for (int x = 0; x < 32; x += 2) {
                     const unsigned long long t2 =
-                        emb::fma_f2(emb::pack_f2(__uint_as_float(sr[c][x]), __uint_as_float(sr[c][x + 1])), scale2, neg_m2);
+                        emb::fma_f2(emb::pack_f2(__uint_as_float(cur[x]), __uint_as_float(cur[x + 1])), scale2, neg_m2);
                     float t0, t1, p0, p1;
                     emb::unpack_f2(t2, t0, t1);
-                    if (POLY_PERIOD > 0 && ((c * 16 + x / 2) % (POLY_PERIOD > 0 ? POLY_PERIOD : 1)) == 0) {
+                    if (POLY_PERIOD > 0 && ((c * 16 + x / 2) % (POLY_PERIOD > 0 ? POLY_PERIOD : 1)) == POLY_PERIOD - 1) {
                         emb::ex2_poly3_pair(t0, t1, p0, p1);  // this pair's exponentials on the FMA pipe, not the SFU
                     } else {
                         p0 = emb::ex2_approx_ftz(t0);
                         p1 = emb::ex2_approx_ftz(t1);
                     }
-                    sum2 = emb::add_f2(sum2, emb::pack_f2(p0, p1));
+                    sum2[(x / 2) & 1] = emb::add_f2(sum2[(x / 2) & 1], emb::pack_f2(p0, p1));
                     packed[x / 2] = pack2<BF16>(p0, p1);
                 }
-                // P over S's own columns: 16-bit pairs, 16 columns per 32 keys
                 asm volatile(
                     "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
                     "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(s_addr + c * 16),
@@ -283,9 +310,15 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
                     "r"(packed[6]), "r"(packed[7]), "r"(packed[8]), "r"(packed[9]), "r"(packed[10]), "r"(packed[11]),
                     "r"(packed[12]), "r"(packed[13]), "r"(packed[14]), "r"(packed[15])
                     : "memory");
+                if (c == 1) {  // the first 64 keys' weights are in place: their half of P V may start
+                    tc::tmem_st_wait();
+                    tc::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) tc::mbar_arrive(&p_half[i]);
+                }
             }
             float sum, sum_hi;
-            emb::unpack_f2(sum2, sum, sum_hi);
+            emb::unpack_f2(emb::add_f2(sum2[0], sum2[1]), sum, sum_hi);
             sum += sum_hi;
             l += sum;
             tc::tmem_st_wait();

@@ -65,13 +65,17 @@ C_TYPES = {"float": "f32", "double": "f64", "int": "i32", "unsigned": "u32", "un
 # emmy_ptx/common.py:55-60
 IDENTITY = {"add": 0.0, "multiply": 1.0, "maximum": -1e30, "minimum": 1e30}
 REDUCE_CANON = {"add": "add", "sum": "add", "multiply": "multiply", "prod": "multiply", "maximum": "maximum",
-                "amax": "maximum", "fmax": "maximum", "minimum": "minimum", "amin": "minimum", "fmin": "minimum"}
+                "amax": "maximum", "fmax": "maximum", "minimum": "minimum", "fmin": "minimum"}
 
 # emmy_ptx/elementwise.py:28-38
 _INT_DTYPES = frozenset({"i16", "i32", "i64", "u8", "u16", "u32", "u64"})
 _INT_OPS = frozenset({"add", "subtract", "multiply", "floor_divide", "remainder", "mod", "left_shift", "right_shift",
                       "bitwise_and", "bitwise_or", "bitwise_xor", "bitwise_count"})
 _WIDTH = {"u8": 8, "i16": 16, "u16": 16, "i32": 32, "u32": 32, "i64": 64, "u64": 64}
+
+
+# Evaluate dot-product loops all trips at once (same additions, same order; see _Blocks.vector_loop).
+VECTOR_LOOPS = True
 
 
 class Unsupported(Exception):
@@ -108,7 +112,10 @@ def run(body, buffers: dict, grid: int, block: int, blocks=None, batch: int | No
     """
     ids = np.arange(grid, dtype=np.int64) if blocks is None else np.asarray(sorted(blocks), np.int64)
     if batch is None:
-        batch = max(1, (1 << 20) // max(1, block))
+        # keep a value near a million elements, counting the extra axis of a vectorised inner loop
+        widest = max([1] + [int(st.axis.extent.as_static()) for st in _all_statements(body)
+                            if type(st).__name__ == "Loop"]) if VECTOR_LOOPS else 1
+        batch = max(1, (1 << 20) // max(1, block * widest))
     for lo in range(0, len(ids), batch):
         part = ids[lo:lo + batch]
         try:
@@ -123,6 +130,15 @@ def run(body, buffers: dict, grid: int, block: int, blocks=None, batch: int | No
 
 def _name(d):
     return None if d is None else getattr(d, "name", d)
+
+
+def _all_statements(stmts):
+    for st in stmts:
+        yield st
+        for field in ("body", "else_body"):
+            child = getattr(st, field, None)
+            if isinstance(child, (tuple, list)):
+                yield from _all_statements(child)
 
 
 class _Blocks:
@@ -218,10 +234,60 @@ class _Blocks:
                 self.bind(st.name, np.asarray(identity).astype(NP[_name(st.dtype) or "f32"]), mask)
 
     def do_Loop(self, s, mask):  # tests/oracle.py:143-147
+        if VECTOR_LOOPS and self.vector_loop(s, mask):
+            return
         self.seed(s, mask)
         for i in range(int(s.axis.extent.as_static())):
             self.bind(s.axis.name, np.int64(i), mask)
             self.run(s.body, mask)
+
+    def vector_loop(self, s, mask) -> bool:
+        """A seeded loop whose body only loads, computes and ends in ONE plain sum (a dot product):
+        all trips are evaluated at once along an extra axis, and the sum is taken by
+        ``np.cumsum`` in the accumulator's type, which adds strictly left to right from the
+        identity 0, i.e. performs the very additions of the trip-by-trip loop in the same order
+        (the parity tests run both forms and compare bit for bit). Returns False when the loop is
+        not of that shape; the caller then runs it trip by trip."""
+        n = int(s.axis.extent.as_static())
+        body = list(s.body)
+        if not s.seed or n < 4 or not body or type(body[-1]).__name__ != "Accum":
+            return False
+        acc = body[-1]
+        if reduce_canon(acc.op.name) != "add" or acc.base is not None or (_name(acc.dtype) or "f32") not in ("f32", "f64"):
+            return False
+        defined, read = [], set()
+        for st in body[:-1]:
+            k = type(st).__name__
+            if k == "Load":
+                defined += list(st.names)
+                for e in st.index:
+                    read |= _expr_names(e)
+            elif k == "Assign":
+                defined.append(st.name)
+                read |= set(st.args)
+            else:
+                return False
+        if acc.name in defined or acc.name in read or acc.value not in defined or s.axis.name in defined:
+            return False
+        sub = _Blocks.__new__(_Blocks)
+        sub.globals, sub.nb, sub.block, sub.shape = self.globals, self.nb, self.block * n, (self.nb, self.block * n)
+        sub.ctaid = self.ctaid
+        sub.tid = np.repeat(self.tid, n, axis=1)
+        sub.row = np.broadcast_to(np.arange(self.nb, dtype=np.int64).reshape(-1, 1), sub.shape)
+        sub.shared, sub.shared_shape = self.shared, self.shared_shape
+        sub.env = {k: np.repeat(v, n, axis=1) for k, v in self.env.items() if k in read and k not in defined}
+        sub.env[s.axis.name] = np.broadcast_to(np.tile(np.arange(n, dtype=np.int64), self.block), sub.shape)
+        wide = np.repeat(mask, n, axis=1)
+        sub.run(body[:-1], wide)
+        t = NP[_name(acc.dtype) or "f32"]
+        v = sub.env[acc.value].reshape(self.nb, self.block, n).astype(t)
+        zero = np.zeros((self.nb, self.block, 1), t)
+        total = np.cumsum(np.concatenate([zero, v], axis=2), axis=2, dtype=t)[:, :, -1]
+        self.bind(acc.name, total, mask)
+        for name in defined:  # the names keep their last trip's values, the loop variable its last index
+            self.bind(name, sub.env[name].reshape(self.nb, self.block, n)[:, :, -1], mask)
+        self.bind(s.axis.name, np.int64(n - 1), mask)
+        return True
 
     def do_StridedLoop(self, s, mask):  # tests/oracle.py:149-166
         self.seed(s, mask)
@@ -352,6 +418,19 @@ class _Blocks:
         root = np.where(mask, slot(np.zeros(self.shape, np.int64)), 0)
         for st, buf in zip(s.state, bufs):
             self.bind(st, buf[self.row, root], mask)
+
+
+def _expr_names(e) -> set:
+    k = type(e).__name__
+    if k == "Var":
+        return {e.name}
+    if k == "BinaryExpr":
+        return _expr_names(e.left) | _expr_names(e.right)
+    if k == "TernaryExpr":
+        return _expr_names(e.cond) | _expr_names(e.if_true) | _expr_names(e.if_false)
+    if k == "CastExpr":
+        return _expr_names(e.expr)
+    return set()
 
 
 def _truth(v):

@@ -43,6 +43,16 @@ def test_restated_interpreter_matches_the_reference_bit_for_bit(golden, name):
         assert same_bits(bufs[k], w), (name, k)
 
 
+@pytest.mark.parametrize("name", [n for n in CASES if n.startswith(("ex_", "wl_", "rand_attention", "rand_shared"))])
+def test_trip_by_trip_loops_give_the_same_as_the_vectorised_dot_products(golden, name, monkeypatch):
+    """The reference's order, one trip after the other, against the all-trips-at-once evaluation."""
+    monkeypatch.setattr(ir_oracle, "VECTOR_LOOPS", False)
+    case, arrays = golden[name]
+    bufs, want = run_case(case, arrays)
+    for k, w in want.items():
+        assert same_bits(bufs[k], w), (name, k)
+
+
 @pytest.mark.parametrize("name", ["ex_a01_attention", "wl_sum_partial", "wl_softmax", "wl_attention"])
 def test_block_at_a_time_order_gives_the_same(golden, name):
     case, arrays = golden[name]
