@@ -190,7 +190,7 @@ def main() -> None:
 
     import torch
     import torch.distributed as dist
-    from emmy_ptx import driver, runner
+    from emmy_ptx import driver, multi, runner
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -224,12 +224,12 @@ def main() -> None:
             finals = [prob.tensors["sum_1"]] + [c["sum_1"] for c in getattr(prob, "copies", [])]
             for i in range(warmup):
                 driver.launch(prob.sets[i % nsets], stream)
-                dist.all_reduce(finals[i % nsets])
+                multi.combine_sum(finals[i % nsets], strict=args.mode == "strict")
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             for i in range(warmup, warmup + steps):
                 driver.launch(prob.sets[i % nsets], stream)
-                dist.all_reduce(finals[i % nsets])
+                multi.combine_sum(finals[i % nsets], strict=args.mode == "strict")
             b.record()
             b.synchronize()
             total_us = a.elapsed_time(b) * 1000.0
@@ -307,7 +307,7 @@ def main() -> None:
                     config=dict(workload=w["describe"], mode=args.mode,
                                 l2=f"inputs larger than L2: passes rotate through {timing['buffer_sets']} buffer sets of "
                                    f"{timing['bytes_per_set'] >> 20} MiB, no flush",
-                                sharding="each rank runs the full workload on its own rows/elements"),
+                                sharding=f"weak: each rank runs the full workload on its own {multi.SHARDED_AXIS[args.workload]}"),
                     roofline=roof, cpu_baseline=cpu, e2e=e2e, gpu_launches=launches, clocks=clocks, families=families,
                     aggregate=dict(value=(w.get("bytes", 0) * world / mean_us / 1e3) if w["bound"] == "hbm" else
                                    (w["flops"] * world / mean_us / 1e6), unit="GB/s" if w["bound"] == "hbm" else "TFLOP/s"))

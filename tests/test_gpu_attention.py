@@ -17,11 +17,14 @@ ULP = {"f16": 2.0 ** -10, "bf16": 2.0 ** -7}
 
 
 def check(got, want, dtype="f16"):
-    """The stated 2e-3 plus the format's allowance above; near zero the scale is the RMS of the output."""
+    """The stated 2e-3 plus the format's allowance above; near zero the scale is the RMS of the output
+    ROW (an output row is a weighted mean of V rows: its small entries carry the rounding of its large ones,
+    and early causal rows are an order of magnitude larger than late ones)."""
     want64 = np.asarray(want, np.float64)
+    got64 = np.asarray(got, np.float64)
     rtol = RTOL + ULP[dtype]
-    atol = rtol * float(np.sqrt(np.mean(want64 ** 2)))
-    assert margin(np.asarray(got, np.float64), want64, rtol, atol) <= 1
+    atol = rtol * np.sqrt(np.mean(want64 ** 2, axis=-1, keepdims=True))
+    assert float(np.max(np.abs(got64 - want64) / (atol + rtol * np.abs(want64)))) <= 1
 
 
 def sampled(batch_heads: int, seq: int):
@@ -87,9 +90,11 @@ def test_attention_full_size_sampled_rows_and_cross_check():
     blocks = sorted({bh * 4096 + r for bh in (0, 77, 255) for r in rows})  # one block per (batch, head, query)
     want = oracle_problem(p, prob.host, blocks=blocks)["attn"].reshape(-1, 128)
     check(got.reshape(-1, 128)[blocks], want[blocks])
-    # the whole tensor against the library attention on the same device (a cross-check, not the oracle)
-    q, k, v = (prob.tensors[n] for n in "qkv")
-    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True).float().cpu().numpy()
-    check(got, ref)
+    # every row of the first and last batch against an f32 attention on the same device (a cross-check,
+    # not the oracle)
+    for b in (0, 7):
+        q, k, v = (prob.tensors[n][b:b + 1].float() for n in "qkv")
+        ref = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True).cpu().numpy()
+        check(got[b:b + 1], ref)
     # the first query of every (batch, head) attends to key 0 only: its output is V[.., 0, :] exactly
     assert np.array_equal(got[:, :, 0, :], prob.host["v"][:, :, 0, :])

@@ -1,0 +1,56 @@
+"""The multi-rank host logic on CPU: two gloo ranks on 127.0.0.1."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from emmy_ptx import multi
+
+
+def test_shards_cover_every_unit_exactly_once():
+    for units, world in [(8192, 8), (256, 3), (5, 8), (1 << 24, 7)]:
+        seen = np.zeros(units, int)
+        for r in range(world):
+            s = multi.shard(units, r, world)
+            seen[s.start:s.stop] += 1
+        assert (seen == 1).all()
+        sizes = [len(multi.shard(units, r, world)) for r in range(world)]
+        assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        multi.shard(10, 2, 2)
+
+
+def _rank(rank, world, port, strict, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    x = np.random.default_rng(0).uniform(-1, 1, 1 << 16).astype(np.float32)
+    mine = multi.shard(x.size, rank, world)
+    partial = torch.tensor([x[mine.start:mine.stop].sum(dtype=np.float32)])
+    total = multi.combine_sum(partial, strict=strict)
+    out.put((rank, float(total.item())))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("strict", [False, True])
+def test_two_ranks_combine_their_partial_sums(strict):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_rank, args=(r, 2, port, strict, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(out.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    x = np.random.default_rng(0).uniform(-1, 1, 1 << 16).astype(np.float32)
+    a, b = x[:1 << 15].sum(dtype=np.float32), x[1 << 15:].sum(dtype=np.float32)
+    assert results[0] == results[1] == float(np.float32(a + b))
