@@ -149,6 +149,9 @@ int launch_one(const emb_launch_t& k, CUstream stream) {
 
 }  // namespace
 
+// for the other translation units of the library: record an error text for the calling thread
+int emb_fail_text(int code, const char* text) { return fail(code, "%s", text); }
+
 extern "C" {
 
 int emb_abi_version(void) { return 2; }

@@ -123,6 +123,30 @@ int emb_time_rotating(const emb_launch_t* launches, int chain_len, int n_sets, v
 int emb_tensor_map(void* map_out, const void* base, int dtype, int rank, const uint64_t* dims,
                    const uint64_t* strides_bytes, const uint32_t* box, int swizzle);
 
+/* The f32 array sum (block partials, then their fold) for callers that cannot
+ * allocate device memory: a plugin inside another framework's memory pool, a
+ * caller in a phase where cudaMalloc's implicit synchronisation is not allowed,
+ * a host with a fixed device-memory budget. It has no counterpart in the
+ * reference. The compiled chain k_sum__partial -> k_sum_1_reduce needs a
+ * caller-owned scratch buffer `sum__partial` of one float per block; this entry
+ * point keeps that scratch in a fixed array inside the library instead
+ * (EMB_STATIC_SUM_MAX_BLOCKS floats = 8 KB, resident on every GPU that loads the
+ * library until the process exits) and calls no allocator of any kind.
+ *   x        n floats on the current device, 16-byte aligned; n a positive multiple of 4
+ *   blocks   CTAs of the first kernel = number of partials; 1..EMB_STATIC_SUM_MAX_BLOCKS,
+ *            anything larger is refused with EMB_E_ARGUMENT and a text
+ *   sum_out  one float on the device
+ * For equal `blocks` the result is bit for bit that of the chain compiled with
+ * --strict (256 threads per block, 16-byte runs, the same butterfly and tree).
+ * The first call on each device looks the array's device address up
+ * (cudaGetSymbolAddress, with that device current): make that first call before
+ * any stream capture begins. All calls on a device share the one array, which
+ * keeps the last call's partials (nothing in it has to start at zero): two calls
+ * whose kernels overlap on the GPU, e.g. on different streams, race on it.
+ * Asynchronous on `stream`. */
+#define EMB_STATIC_SUM_MAX_BLOCKS 2048
+int emb_array_sum_f32_static(const float* x, uint64_t n, uint32_t blocks, float* sum_out, void* stream);
+
 /* Text of the last error on the calling thread ("" if none). */
 const char* emb_last_error(void);
 
