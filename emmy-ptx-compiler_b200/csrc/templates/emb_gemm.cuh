@@ -23,6 +23,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "emb_math.cuh"
 #include "emb_tc.cuh"
 
 namespace emb {
@@ -44,9 +45,23 @@ struct GemmShape {
     int m, n, k;
 };
 
-template <int STAGES, int GROUP_M, bool BF16>
+// What the epilogue does to an accumulator before it is rounded to the output type.
+enum GemmEpilogue : int {
+    EPI_NONE = 0,        // c = acc
+    EPI_SCALE = 1,       // c = acc * scale[0]
+    EPI_SCALE_GELU = 2,  // c = gelu_tanh(acc * scale[0])
+};
+
+template <int EPI> __device__ __forceinline__ float gemm_epilogue(float acc, float scale) {
+    if (EPI == EPI_SCALE) return acc * scale;
+    if (EPI == EPI_SCALE_GELU) return gelu_tanh_fast(acc * scale);
+    return acc;
+}
+
+template <int STAGES, int GROUP_M, bool BF16, int EPI = EPI_NONE>
 __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ map_a, const CUtensorMap* __restrict__ map_b,
-                                               void* __restrict__ c_out, GemmShape shape, unsigned* status) {
+                                               void* __restrict__ c_out, GemmShape shape, unsigned* status,
+                                               const float* __restrict__ scale_ptr = nullptr) {
     constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
     constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr uint32_t TMEM_COLS = 512;
@@ -153,6 +168,7 @@ __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ m
         uint32_t local = 0;
         out_t* c = static_cast<out_t*>(c_out);
         const bool vec_ok = (shape.n % 8) == 0;
+        const float scale = (EPI != EPI_NONE && scale_ptr) ? __ldg(scale_ptr) : 1.0f;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
             int tm, tn;
             tile_coords(t, tm, tn);
@@ -166,6 +182,10 @@ __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ m
                 uint32_t r[32];
                 tc::tmem_ld_32x32(taddr + cb, r);
                 tc::tmem_ld_wait();
+                if (EPI != EPI_NONE) {
+#pragma unroll
+                    for (int x = 0; x < 32; ++x) r[x] = __float_as_uint(gemm_epilogue<EPI>(__uint_as_float(r[x]), scale));
+                }
                 const int col = tn * BN + cb;
                 if (row < shape.m) {
                     out_t* dst = c + static_cast<size_t>(row) * shape.n + col;

@@ -53,6 +53,7 @@ class Plan:
     smem_bytes: int | None = None
     extra_params: list = field(default_factory=list)  # tensor maps and scratch the launch header lists
     nvcc_flags: tuple = ()
+    pre: list = field(default_factory=list)  # launches of auxiliary entries of the same module, run before the main one
 
 
 def need(cond, why: str) -> None:

@@ -117,30 +117,48 @@ class CompiledKernel:
         self.module = driver.Module(cubin)
         self.function = self.module.function(meta["entry"])
 
-    def bind(self, tensors: dict) -> driver.Launch:
-        """A launch of this kernel on ``tensors`` (name -> torch tensor). A ``status`` parameter (the
-        word a kernel's bounded waits report into) gets its own zeroed tensor, kept in ``tensors``
-        under ``"<entry>.status"`` and read by ``check_status``."""
+    def bind(self, tensors: dict) -> list:
+        """The launches of this kernel on ``tensors`` (name -> torch tensor), in order: the auxiliary
+        entries its launch header lists under ``pre``, then the kernel itself. Parameters that are not
+        arguments of meta.json get their own tensors, kept in ``tensors`` under ``"<entry>.<name>"``: a
+        zeroed ``status`` word (what the kernel's bounded waits report into, read by ``check_status``)
+        and ``scratch`` buffers (device memory between the kernels of one module)."""
         import torch
+        entry = self.meta["entry"]
+        anchor = next(iter(tensors.values()))
+
+        def own(name, make):
+            key = f"{entry}.{name}"
+            if key not in tensors:
+                tensors[key] = make()
+            return tensors[key]
+
+        def resolve(name):
+            return tensors[name] if name in tensors else tensors[f"{entry}.{name}"]
+
+        def one(fn, li):
+            params = []
+            for p in li["params"]:
+                if p["kind"] == "buffer":
+                    params.append(resolve(p["name"]).data_ptr())
+                elif p["kind"] == "status":
+                    params.append(own("status", lambda: torch.zeros(4, dtype=torch.int32, device=anchor.device)).data_ptr())
+                elif p["kind"] == "scratch":
+                    params.append(own(p["name"], lambda: torch.empty(p["bytes"], dtype=torch.uint8, device=anchor.device)).data_ptr())
+                elif p["kind"] == "tmap":
+                    t = resolve(p["buffer"])
+                    params.append(driver.TensorMap(t.data_ptr() + p.get("offset_bytes", 0), p["dtype"], p["dims"],
+                                                   p["strides_bytes"], p["box"], p.get("swizzle", "128B")))
+                else:
+                    raise ValueError(f"unknown parameter kind {p['kind']!r}")
+            flags = driver.LAUNCH_PDL if li.get("pdl") else 0
+            return driver.Launch(fn, li["grid"], li["block"], li.get("cluster", 1), li.get("smem_bytes", 0), params, flags)
+
         li = self.launch_info
-        params = []
-        for p in li["params"]:
-            if p["kind"] == "buffer":
-                params.append(tensors[p["name"]].data_ptr())
-            elif p["kind"] == "status":
-                key = f"{self.meta['entry']}.status"
-                if key not in tensors:
-                    anchor = next(iter(tensors.values()))
-                    tensors[key] = torch.zeros(4, dtype=torch.int32, device=anchor.device)
-                params.append(tensors[key].data_ptr())
-            elif p["kind"] == "tmap":
-                t = tensors[p["buffer"]]
-                params.append(driver.TensorMap(t.data_ptr() + p.get("offset_bytes", 0), p["dtype"], p["dims"], p["strides_bytes"],
-                                               p["box"], p.get("swizzle", "128B")))
-            else:
-                raise ValueError(f"unknown parameter kind {p['kind']!r}")
-        flags = driver.LAUNCH_PDL if li.get("pdl") else 0
-        return driver.Launch(self.function, li["grid"], li["block"], li.get("cluster", 1), li.get("smem_bytes", 0), params, flags)
+        # scratch must exist before a tensor map over it is built: make them in the order the header lists them
+        out = [one(self.module.function(pre["entry"]), pre) for pre in li.get("pre", ())]
+        out.append(one(self.function, li))
+        return out
 
 
 class Problem:
@@ -174,7 +192,7 @@ class Problem:
                 else:
                     self.host[name] = given[name]
                     self.tensors[name] = to_torch(given[name], a["dtype"], self.device)
-        self.launches = [k.bind(self.tensors) for k in self.kernels]
+        self.launches = [l for k in self.kernels for l in k.bind(self.tensors)]
         self.sets = [self.launches]  # further copies of every buffer, for cold-cache timing (rotate())
         self.zero = [n for k in self.meta["kernels"] for n in k.get("zero_outputs", ())]
 
@@ -195,9 +213,10 @@ class Problem:
 
     def check_status(self) -> None:
         """Raise if a kernel's bounded wait gave up (its status word is non-zero)."""
+        import torch
         for tensors in [self.tensors] + list(getattr(self, "copies", [])):
             for name, t in tensors.items():
-                if name.endswith(".status"):
+                if name.endswith(".status") and t.dtype == torch.int32:
                     word = t.cpu().tolist()
                     if word[0]:
                         where = {1: "shared-memory stage never filled", 2: "shared-memory stage never released",
@@ -223,7 +242,7 @@ class Problem:
         while len(self.sets) < want:
             clone = {n: t.clone() for n, t in self.tensors.items()}
             self.copies.append(clone)
-            self.sets.append([k.bind(clone) for k in self.kernels])
+            self.sets.append([l for k in self.kernels for l in k.bind(clone)])
         return len(self.sets)
 
     def time_rotating_us(self, warmup: int = 3, iters: int = 20, only=None, batch: int = 1) -> list:

@@ -250,5 +250,128 @@ def match_attention(src, strict: bool) -> Plan:
     return Plan("blocking", source, remarks, grid=grid, block=threads, smem_bytes=smem, extra_params=extra)
 
 
-def match_mlp(src, strict: bool):
-    raise Refusal("not built yet")
+# ---------------------------------------------------------------- fused GELU MLP
+
+GELU_OPS = ["multiply", "multiply", "multiply", "multiply", "add", "multiply", "tanh", "add", "multiply", "multiply"]
+
+
+def match_mlp(src, strict: bool) -> Plan:
+    """y = (gelu_tanh((x . w1) s1) . w2) s2 in emmy's column-recomputing form (examples/k_gelu_mlp/
+    k_matmul_reduce_6918c9.ir.txt, tests/kernels.py:99-122): thread (row, column, lane) walks the hidden
+    units lane, lane + L, ..., recomputes h = x[row, :] . w1[:, unit] for each (the work the reference's cluster
+    rewrite shares, emmy_ptx/cluster.py:120-164), applies GELU, folds g * w2[unit, column]; the L lanes combine
+    by butterfly. Weights are e4m3 codes decoded by from_f8e4m3 with per-tensor f32 scales."""
+    tile = single_tile(src)
+    need(len(tile.axes) == 3, "the Tile is not over (row, column, lane) cells")
+    row, col, lane = (a.name for a in tile.axes)
+    T, D, L = (a.extent.as_static() for a in tile.axes)
+    body = list(tile.body)
+    scalars = {}
+    while body and kind(body[0]) == "Load":
+        ld = body.pop(0)
+        buf = src.buffers.get(ld.input)
+        need(buf is not None and math.prod(buf.shape) == 1 and len(ld.names) == 1, "a leading Load is not of a scalar")
+        scalars[ld.names[0]] = ld.input
+    need(len(body) == 4 and [kind(s) for s in body] == ["StridedLoop", "WarpShuffle", "Assign", "Cond"],
+         "the cell is not hidden loop, butterfly, scale, guarded Write")
+    outer, shuffle, scale_y, cond = body
+    need(outer.seed and outer.end is None and is_var(outer.start, lane) and kind(outer.step) == "Literal"
+         and outer.step.value == L, "the hidden loop is not lane, lane + L, ...")
+    Hd = outer.axis.extent.as_static()
+    h_axis = outer.axis.name
+    ob = list(outer.body)
+    need(len(ob) == 1 + len(GELU_OPS) + 4 and kind(ob[0]) == "Loop", "the hidden loop's body is not dot product, GELU, fold")
+    inner = ob[0]
+    k_axis = inner.axis.name
+    need(inner.seed and inner.axis.extent.as_static() == D and [kind(s) for s in inner.body] == ["Load", "Load", "Assign", "Assign", "Accum"],
+         "the dot product is not Load x, Load w1, decode, multiply, Accum")
+    lx, lw, dec, mul, acc0 = inner.body
+    need(len(lx.index) == 2 and is_var(lx.index[0], row) and is_var(lx.index[1], k_axis) and dtype_name(lx.dtype) == "f32",
+         "x is not read as f32 at [row, k]")
+    need(len(lw.index) == 2 and is_var(lw.index[0], k_axis) and is_var(lw.index[1], h_axis), "w1 is not read at [k, unit]")
+    need(dec.op.name == "from_f8e4m3" and tuple(dec.args) == (lw.names[0],) and mul.op.name == "multiply"
+         and set(mul.args) == {dec.name, lx.names[0]} and acc0.value == mul.name and acc0.base is None
+         and codegen.CANON.get(acc0.op.name) == "add", "the dot product does not decode w1 and sum x * w1 in f32")
+    gelu = ob[1:1 + len(GELU_OPS)]
+    need(all(kind(s) == "Assign" for s in gelu) and [s.op.name for s in gelu] == GELU_OPS, "the activation is not the tanh-form GELU")
+    hp, h2, h3, t0, t1, t2, th, t3, t4, g = gelu
+    consts = {n: src.constants.get(b) for n, b in scalars.items()}
+
+    def const(name, value):
+        return name in consts and consts[name] is not None and abs(consts[name] - value) <= 1e-6 * abs(value)
+    s1 = [a for a in hp.args if a != acc0.name]
+    need(acc0.name in hp.args and len(s1) == 1 and s1[0] in scalars, "h is not the dot product times a scalar scale")
+    need(set(h2.args) == {hp.name} and set(h3.args) == {h2.name, hp.name} and h3.name in t0.args
+         and any(const(a, 0.044715) for a in t0.args) and set(t1.args) == {hp.name, t0.name} and t1.name in t2.args
+         and any(const(a, math.sqrt(2 / math.pi)) for a in t2.args) and tuple(th.args) == (t2.name,)
+         and th.name in t3.args and any(const(a, 1.0) for a in t3.args) and hp.name in t4.args
+         and any(const(a, 0.5) for a in t4.args) and set(g.args) == {t3.name, t4.name},
+         "the activation's constants or wiring are not 0.5 h (1 + tanh(sqrt(2/pi) (h + 0.044715 h^3)))")
+    lw2, dec2, mul2, acc1 = ob[1 + len(GELU_OPS):]
+    need(kind(lw2) == "Load" and len(lw2.index) == 2 and is_var(lw2.index[0], h_axis) and is_var(lw2.index[1], col)
+         and kind(dec2) == "Assign" and dec2.op.name == "from_f8e4m3" and tuple(dec2.args) == (lw2.names[0],)
+         and kind(mul2) == "Assign" and mul2.op.name == "multiply" and set(mul2.args) == {dec2.name, g.name}
+         and kind(acc1) == "Accum" and acc1.value == mul2.name and acc1.base is None and codegen.CANON.get(acc1.op.name) == "add",
+         "the second fold is not sum over units of g * decode(w2[unit, column])")
+    need(tuple(shuffle.state) == (acc1.name,) and int(shuffle.length) == L and len(shuffle.combine_states) == 1
+         and codegen.CANON.get(shuffle.combine_states[0].op.name) == "add", "the lanes do not add their partial sums")
+    s2 = [a for a in scale_y.args if a != acc1.name]
+    need(scale_y.op.name == "multiply" and acc1.name in scale_y.args and len(s2) == 1 and s2[0] in scalars, "y is not the sum times a scalar scale")
+    from .families import eq_zero
+    need(eq_zero(cond.cond, lane) and len(cond.body) == 1 and kind(cond.body[0]) == "Write" and not cond.else_body,
+         "the result is not written by lane 0")
+    w = cond.body[0]
+    need(tuple(w.values) == (scale_y.name,) and len(w.index) == 2 and is_var(w.index[0], row) and is_var(w.index[1], col)
+         and not w.atomic, "the Write is not y[row, column]")
+    X, W1, W2, Y = (src.buffers.get(n) for n in (lx.input, lw.input, lw2.input, w.output))
+    need(all(b is not None for b in (X, W1, W2, Y)), "unknown buffers")
+    need(X.dtype == "bf16" and Y.dtype == "bf16" and W1.dtype == "f8e4m3" and W2.dtype == "f8e4m3",
+         "not bf16 activations with e4m3 weights")
+    need(tuple(X.shape) == (T, D) and tuple(W1.shape) == (D, Hd) and tuple(W2.shape) == (Hd, D) and tuple(Y.shape) == (T, D),
+         "buffer shapes do not fit the cells")
+    need(Hd % L == 0, "the hidden units do not divide among the lanes")
+    need(not ({lx.input, lw.input, lw2.input} & set(src.written)), "the kernel writes an operand")
+    need(not strict, "the tensor cores sum in their own order and h is rounded to bf16 between the products (--strict keeps the IR's)")
+    need(D % 8 == 0 and Hd % 8 == 0, "row strides are not multiples of 16 bytes")
+
+    e = src.name
+    s1_buf, s2_buf = scalars[s1[0]], scalars[s2[0]]
+    stage = (128 + 256) * 64 * 2
+    smem = GEMM_STAGES * stage + 1024 + 256
+    tiles1 = math.ceil(T / 128) * math.ceil(Hd / 256)
+    tiles2 = math.ceil(T / 128) * math.ceil(D / 256)
+    sig = codegen.signature(src)
+    lines = ['#include "emb_gemm.cuh"', '#include "emb_dequant.cuh"',
+             f'extern "C" __global__ void __launch_bounds__(256) {e}__w1(const unsigned char* __restrict__ codes, __nv_bfloat16* __restrict__ out) {{',
+             f"    emb::dequant_transpose_e4m3(codes, out, {D}, {Hd});", "}",
+             f'extern "C" __global__ void __launch_bounds__(256) {e}__w2(const unsigned char* __restrict__ codes, __nv_bfloat16* __restrict__ out) {{',
+             f"    emb::dequant_transpose_e4m3(codes, out, {Hd}, {D});", "}",
+             f'extern "C" __global__ void __launch_bounds__(192, 1) {e}__h(const __grid_constant__ CUtensorMap tmap_x, '
+             "const __grid_constant__ CUtensorMap tmap_w1t, __nv_bfloat16* __restrict__ h, const float* __restrict__ scale, "
+             "unsigned* __restrict__ status) {",
+             f"    emb::gemm_tn_kernel<{GEMM_STAGES}, {GEMM_GROUP_M}, true, emb::EPI_SCALE_GELU>(&tmap_x, &tmap_w1t, h, "
+             f"emb::GemmShape{{{T}, {Hd}, {D}}}, status, scale);", "}",
+             f'extern "C" __global__ void __launch_bounds__(192, 1) {e}({sig}, const __grid_constant__ CUtensorMap tmap_h, '
+             "const __grid_constant__ CUtensorMap tmap_w2t, unsigned* __restrict__ status) {",
+             f"    emb::gemm_tn_kernel<{GEMM_STAGES}, {GEMM_GROUP_M}, true, emb::EPI_SCALE>(&tmap_h, &tmap_w2t, p_{w.output}, "
+             f"emb::GemmShape{{{T}, {D}, {Hd}}}, status, p_{s2_buf});", "}"]
+    pre = [
+        dict(entry=f"{e}__w1", grid=[math.ceil(D / 64) * math.ceil(Hd / 64), 1, 1], block=[256, 1, 1], cluster=1, smem_bytes=0,
+             params=[dict(kind="buffer", name=lw.input), dict(kind="scratch", name="w1t", bytes=Hd * D * 2)]),
+        dict(entry=f"{e}__w2", grid=[math.ceil(Hd / 64) * math.ceil(D / 64), 1, 1], block=[256, 1, 1], cluster=1, smem_bytes=0,
+             params=[dict(kind="buffer", name=lw2.input), dict(kind="scratch", name="w2t", bytes=D * Hd * 2)]),
+        dict(entry=f"{e}__h", grid=[min(TARGET_SMS, tiles1), 1, 1], block=[192, 1, 1], cluster=1, smem_bytes=smem,
+             params=[tmap("x", lx.input, "bf16", (D, T), (D * 2,), (64, 128)), tmap("w1t", "w1t", "bf16", (D, Hd), (D * 2,), (64, 256)),
+                     dict(kind="scratch", name="h", bytes=T * Hd * 2), dict(kind="buffer", name=s1_buf), dict(kind="status", name="status")]),
+    ]
+    extra = [tmap("h", "h", "bf16", (Hd, T), (Hd * 2,), (64, 128)), tmap("w2t", "w2t", "bf16", (Hd, D), (Hd * 2,), (64, 256)),
+             dict(kind="status", name="status")]
+    remarks = [f"MLP template: {T} tokens, d_model {D}, hidden {Hd}; the e4m3 weights are decoded once to bf16 (exactly) and "
+               "transposed to K-major, then two tcgen05 matmuls: h = gelu_tanh(s1 x w1) with the activation in the first one's "
+               "epilogue (h kept in bf16), y = s2 h w2",
+               f"four launches from one module: {e}__w1, {e}__w2 (decode), {e}__h ({tiles1} tiles), {e} ({tiles2} tiles); "
+               f"scratch: {(2 * Hd * D * 2 + T * Hd * 2) >> 20} MiB",
+               "the recomputation of h by every (column, lane) thread of the IR is shared by construction; the cluster / "
+               "shared-memory exchange of the reference's rewrite is not used (h goes through L2 / HBM once)"]
+    return Plan("clusters", "\n".join(lines) + "\n", remarks, grid=min(TARGET_SMS, tiles2), block=192, smem_bytes=smem,
+                extra_params=extra, pre=pre)

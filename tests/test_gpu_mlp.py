@@ -1,0 +1,73 @@
+"""GPU parity of the GELU-MLP template (e4m3 weight decode, two tcgen05 matmuls, GELU in the first epilogue)."""
+
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from emmy_ptx import problems, runner
+from helpers import oracle_problem
+
+pytestmark = pytest.mark.gpu
+RTOL = 3e-2  # the stated tolerance for per-tensor-scaled fp8 weights
+
+
+def check(got, want, rtol=RTOL):
+    want64, got64 = np.asarray(want, np.float64), np.asarray(got, np.float64)
+    atol = rtol * np.sqrt(np.mean(want64 ** 2))
+    m = float(np.max(np.abs(got64 - want64) / (atol + rtol * np.abs(want64))))
+    assert m <= 1, m
+    return m
+
+
+def reference(host):
+    """The float64 expression the problem's `code` names."""
+    import ml_dtypes
+    w1 = host["w1"].view(ml_dtypes.float8_e4m3fn).astype(np.float64) * float(host["w1_scale"][0])
+    w2 = host["w2"].view(ml_dtypes.float8_e4m3fn).astype(np.float64) * float(host["w2_scale"][0])
+    h = host["x"].astype(np.float64) @ w1
+    g = 0.5 * h * (1 + np.tanh(problems.GELU_C * (h + problems.GELU_K * h ** 3)))
+    return g @ w2
+
+
+@pytest.mark.parametrize("tokens,d_model,hidden", [(128, 256, 256), (256, 512, 1024), (200, 264, 328)])
+def test_mlp_small_against_the_oracle(tmp_path, tokens, d_model, hidden):
+    block = 64
+    p = problems.gelu_mlp(tokens=tokens, d_model=d_model, hidden=hidden, lanes=8, block=block, ident="t")
+    prob = runner.Problem(problems.write(p, tmp_path), "optimized")
+    assert prob.kernels[0].launch_info["family"] == "clusters" and len(prob.launches) == 4
+    got = prob.run()["mlp"]
+    grid = p["kernels"][0]["grid"]
+    blocks = sorted(set(np.random.default_rng(3).integers(0, grid, 48).tolist()) | {0, grid - 1})
+    want = oracle_problem(p, prob.host, blocks=blocks)["mlp"].reshape(-1)
+    cells = np.concatenate([np.arange(b * block // 8, (b + 1) * block // 8) for b in blocks])
+    # bf16 output of sums of O(100) terms: well inside the fp8 tolerance; the measured margin is far below 1
+    assert check(got.reshape(-1)[cells], want[cells]) < 0.5
+    check(got, reference(prob.host))
+
+
+def test_mlp_statement_lowering_matches_too(tmp_path):
+    p = problems.gelu_mlp(tokens=8, d_model=64, hidden=64, lanes=8, block=64, ident="t")
+    prob = runner.Problem(problems.write(p, tmp_path), "strict")
+    assert prob.kernels[0].launch_info["family"] == "statements"
+    got = prob.run()["mlp"]
+    want = oracle_problem(p, prob.host)["mlp"]
+    check(got, want, rtol=2e-3 + 2.0 ** -8)
+
+
+def test_mlp_full_size_sampled_cells_and_cross_check():
+    import torch
+    folder = Path(runner.__file__).resolve().parent.parent / "problems" / "k_mlp_gelu_tanh_16384x4096x16384"
+    prob = runner.Problem(folder, "optimized")
+    got = prob.run()["mlp"]
+    p = problems.gelu_mlp()
+    blocks = [123457]  # 256 threads = 32 output cells; every thread walks 2048 hidden units of 4096-long dot products
+    want = oracle_problem(p, prob.host, blocks=blocks)["mlp"].reshape(-1)
+    cells = np.arange(blocks[0] * 32, blocks[0] * 32 + 32)
+    check(got.reshape(-1)[cells], want[cells])
+    # the whole tensor against f32 matmuls on the same device (a cross-check, not the oracle)
+    x = prob.tensors["x"].float()
+    w1 = prob.tensors["w1"].view(torch.float8_e4m3fn).float() * prob.tensors["w1_scale"]
+    w2 = prob.tensors["w2"].view(torch.float8_e4m3fn).float() * prob.tensors["w2_scale"]
+    ref = (torch.nn.functional.gelu(x @ w1, approximate="tanh") @ w2).cpu().numpy()
+    check(got, ref)
