@@ -116,8 +116,23 @@ class ClockSampler(threading.Thread):
                     samples=len(self.samples))
 
 
+_JOB = None  # (body, buffers, grid, block) of the oracle run the forked workers share
+
+
+def _oracle_share(blocks):
+    from oracle import ir_oracle
+    body, bufs, grid, block = _JOB
+    ir_oracle.run(body, bufs, grid, block, blocks=blocks)
+    return len(blocks)
+
+
 def oracle_sample(workload: str, budget_s: float, workers: int) -> dict:
-    """Time the oracle on a bounded sample of the workload's blocks and extrapolate to the grid."""
+    """Time the oracle on a bounded sample of the workload's blocks and extrapolate to the grid.
+    ``workers`` > 1 interprets disjoint shares of the sample in that many forked processes (blocks are
+    independent in the interpreter)."""
+    global _JOB
+    import multiprocessing as mp
+
     import numpy as np
     from emmy_ptx import problems, runner
     from oracle import ir_oracle
@@ -128,30 +143,32 @@ def oracle_sample(workload: str, budget_s: float, workers: int) -> dict:
     host = None
     for kern, km in zip(p["kernels"], meta_args):
         grid, block = kern["grid"], kern["block"]
-        # inputs: small synthetic stand-ins of the right shapes are not enough for the interpreter (it indexes the
-        # real buffers), so the real host inputs are generated once
-        if host is None:
+        if host is None:  # the interpreter indexes the real buffers: generate the real inputs once
             host = runner.host_inputs(km["args"])
         bufs = dict(host)
-        name, shape, dt = kern["output"]
-        bufs[name] = np.zeros(shape, runner.numpy_dtype(dt))
         for k2 in p["kernels"]:
             n2, s2, d2 = k2["output"]
             bufs.setdefault(n2, np.zeros(s2, runner.numpy_dtype(d2)))
-        probe = max(1, min(grid, 4))
+        probe = max(1, min(grid, 2))
         t0 = time.perf_counter()
         ir_oracle.run(kern["body"], bufs, grid, block, blocks=range(probe))
         per_block = (time.perf_counter() - t0) / probe
-        sample = int(max(probe, min(grid, budget_s / max(per_block, 1e-9) / len(p["kernels"]))))
+        sample = int(max(probe, min(grid, workers * budget_s / max(per_block, 1e-9) / len(p["kernels"]))))
         step = max(1, grid // sample)
         blocks = list(range(0, grid, step))[:sample]
+        used = max(1, min(workers, len(blocks)))
         t0 = time.perf_counter()
-        ir_oracle.run(kern["body"], bufs, grid, block, blocks=blocks)
+        if used == 1:
+            ir_oracle.run(kern["body"], bufs, grid, block, blocks=blocks)
+        else:
+            _JOB = (kern["body"], bufs, grid, block)
+            with mp.get_context("fork").Pool(used) as pool:
+                pool.map(_oracle_share, [blocks[i::used] for i in range(used)])
         dt_s = time.perf_counter() - t0
         total_us += dt_s / len(blocks) * grid * 1e6
-        notes.append(f"{kern['entry']}: {len(blocks)} of {grid} CTAs interpreted in {dt_s:.1f} s, scaled to the grid")
-    return dict(value=total_us, unit="us", cores=1, kind="port", sample="; ".join(notes) +
-                " (oracle/ir_oracle.py, numpy, one thread; extrapolated)")
+        notes.append(f"{kern['entry']}: {len(blocks)} of {grid} CTAs interpreted in {dt_s:.1f} s on {used} core(s), scaled to the grid")
+    return dict(value=total_us, unit="us", cores=max(1, workers), kind="port", sample="; ".join(notes) +
+                " (oracle/ir_oracle.py: numpy restatement of the reference's interpreter; extrapolated)")
 
 
 def reference_arm(args) -> None:
@@ -163,7 +180,7 @@ def reference_arm(args) -> None:
     vals = []
     base = None
     for _ in range(min(steps, 3)):  # each step is a bounded sample; more than a few repeats adds nothing
-        base = oracle_sample(args.workload, budget_s=8.0, workers=1)
+        base = oracle_sample(args.workload, budget_s=8.0, workers=os.cpu_count() or 1)
         vals.append(base["value"])
     value = statistics.median(vals)
     base["value"] = value

@@ -1,0 +1,98 @@
+"""The tensor-core matchers: what they take, what their launch header carries, and when they refuse."""
+
+import json
+import re
+
+import pytest
+
+from emmy_ptx import compile_file, families, frontend, ir, problems, tcfamilies
+
+
+def load(tmp_path, problem, entry):
+    return frontend.load(problems.write(problem, tmp_path) / f"{entry}.ir.json")
+
+
+def rebuilt(src, edit):
+    tile = src.body[0]
+    return frontend.KernelSource(src.name, (tile.replace(body=tuple(edit(list(tile.body)))),), src.params, src.buffers,
+                                 src.launch, src.written, src.constants, src.meta)
+
+
+def launch_of(ptx):
+    return json.loads(re.search(r"^// launch: (.*)$", ptx, re.M).group(1))
+
+
+def test_matmul_is_taken_and_described(tmp_path):
+    folder = problems.write(problems.matmul_f16(m=256, n=512, k=128, ident="m"), tmp_path)
+    ptx = compile_file(str(folder / "k_matmul.ir.json"))
+    li = launch_of(ptx)
+    assert li["family"] == "tensorcore" and li["block"] == [192, 1, 1] and li["grid"] == [4, 1, 1]
+    kinds = [p["kind"] for p in li["params"]]
+    assert kinds == ["buffer", "buffer", "buffer", "tmap", "tmap", "status"]
+    a, b = li["params"][3], li["params"][4]
+    assert a["dims"] == [128, 256] and a["box"] == [64, 128] and b["dims"] == [128, 512] and b["box"] == [64, 256]
+    assert "tcgen05.mma" in ptx and "cp.async.bulk.tensor.2d" in ptx and "multicast" not in ptx.split("\n.version")[1]
+    assert launch_of(compile_file(str(folder / "k_matmul.ir.json"), strict=True))["family"] == "statements"
+
+
+def test_matmul_refusals(tmp_path):
+    src = load(tmp_path, problems.matmul_f16(m=256, n=512, k=128, ident="m"), "k_matmul")
+    with pytest.raises(families.Refusal, match="own order"):
+        tcfamilies.match_matmul(src, True)
+    # B indexed [k, n]: row-major B is not what the template loads
+    def swap(b):
+        loop = b[0]
+        lb = loop.body[1]
+        return [loop.replace(body=(loop.body[0], lb.replace(index=(lb.index[1], lb.index[0])), *loop.body[2:])), b[1]]
+    with pytest.raises(families.Refusal, match="row-major A, column-major B"):
+        tcfamilies.match_matmul(rebuilt(src, swap), False)
+    # an f16 product (no dtype on the multiply) is not the f32 accumulation the tensor cores do
+    def f16_product(b):
+        loop = b[0]
+        mul = loop.body[2]
+        return [loop.replace(body=(*loop.body[:2], mul.replace(dtype=None), loop.body[3])), b[1]]
+    with pytest.raises(families.Refusal, match="f32 multiply"):
+        tcfamilies.match_matmul(rebuilt(src, f16_product), False)
+    odd = load(tmp_path, problems.matmul_f16(m=256, n=512, k=100, ident="odd"), "k_matmul")
+    with pytest.raises(families.Refusal, match="16 bytes"):
+        tcfamilies.match_matmul(odd, False)
+
+
+def test_attention_is_taken_and_refused(tmp_path):
+    src = load(tmp_path, problems.attention(batch=1, heads=2, seq=256, dim=128, ident="a"), "k_attention")
+    plan = tcfamilies.match_attention(src, False)
+    assert plan.family == "blocking" and plan.grid == 2 and plan.block == 320 and "attention_fwd_kernel<2, true, false" in plan.source
+    full = load(tmp_path, problems.attention(batch=1, heads=1, seq=128, dim=128, causal=False, ident="b"), "k_attention")
+    plan = tcfamilies.match_attention(full, False)
+    assert plan.block == 192 and "attention_fwd_kernel<1, false, false" in plan.source
+    with pytest.raises(families.Refusal, match="own order"):
+        tcfamilies.match_attention(src, True)
+    short = load(tmp_path, problems.attention(batch=1, heads=1, seq=96, dim=128, ident="c"), "k_attention")
+    with pytest.raises(families.Refusal, match="multiple of the 128-row tile"):
+        tcfamilies.match_attention(short, False)
+    narrow = load(tmp_path, problems.attention(batch=1, heads=1, seq=128, dim=64, ident="d"), "k_attention")
+    with pytest.raises(families.Refusal, match="head dimension"):
+        tcfamilies.match_attention(narrow, False)
+    # the maximum must move LAST: an update that moves m before the sums read it is not the online softmax
+    def early_max(b):
+        loop = next(s for s in b if ir.kind(s) == "StridedLoop")
+        body = list(loop.body)
+        body.insert(2, body.pop())
+        return [loop.replace(body=tuple(body)) if s is loop else s for s in b]
+    with pytest.raises(families.Refusal, match="maximum does not move last"):
+        tcfamilies.match_attention(rebuilt(src, early_max), False)
+
+
+def test_mlp_is_taken_with_its_chain_and_refused(tmp_path):
+    src = load(tmp_path, problems.gelu_mlp(tokens=128, d_model=256, hidden=512, lanes=8, block=64, ident="k"), "k_mlp_gelu")
+    plan = tcfamilies.match_mlp(src, False)
+    assert plan.family == "clusters" and [p["entry"] for p in plan.pre] == ["k_mlp_gelu__w1", "k_mlp_gelu__w2", "k_mlp_gelu__h"]
+    scratch = {p["name"]: p["bytes"] for pre in plan.pre for p in pre["params"] if p["kind"] == "scratch"}
+    assert scratch == {"w1t": 512 * 256 * 2, "w2t": 256 * 512 * 2, "h": 128 * 512 * 2}
+    with pytest.raises(families.Refusal, match="own order"):
+        tcfamilies.match_mlp(src, True)
+    # a different activation constant is not the tanh-form GELU
+    wrong = frontend.KernelSource(src.name, src.body, src.params, src.buffers, src.launch, src.written,
+                                  {**src.constants, "gelu_k": 0.05}, src.meta)
+    with pytest.raises(families.Refusal, match="constants or wiring"):
+        tcfamilies.match_mlp(wrong, False)
