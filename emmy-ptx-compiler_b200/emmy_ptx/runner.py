@@ -142,7 +142,7 @@ class CompiledKernel:
                 if p["kind"] == "buffer":
                     params.append(resolve(p["name"]).data_ptr())
                 elif p["kind"] == "status":
-                    params.append(own("status", lambda: torch.zeros(4, dtype=torch.int32, device=anchor.device)).data_ptr())
+                    params.append(own("status", lambda: torch.zeros(8, dtype=torch.int32, device=anchor.device)).data_ptr())
                 elif p["kind"] == "scratch":
                     params.append(own(p["name"], lambda: torch.empty(p["bytes"], dtype=torch.uint8, device=anchor.device)).data_ptr())
                 elif p["kind"] == "tmap":
@@ -280,7 +280,7 @@ def run_source(src, arrays: dict, mode: str = "optimized", device: int = 0) -> d
         if p["kind"] == "buffer":
             params.append(tensors[p["name"]].data_ptr())
         elif p["kind"] == "status":
-            status = torch.zeros(4, dtype=torch.int32, device=dev)
+            status = torch.zeros(8, dtype=torch.int32, device=dev)
             params.append(status.data_ptr())
         else:
             t = tensors[p["buffer"]]

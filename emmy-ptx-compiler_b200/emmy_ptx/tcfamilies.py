@@ -31,7 +31,7 @@ from .ir import dtype_name, kind
 TARGET_SMS = 148
 GEMM_STAGES = 4
 GEMM_GROUP_M = 16
-ATTN_POLY_PERIOD = 0  # every n-th pair of softmax weights gets its 2^x from an FMA polynomial instead of the SFU (0: none)
+ATTN_POLY_PERIOD = 4  # every n-th pair of softmax weights gets its 2^x from an FMA polynomial instead of the SFU (0: none)
 
 
 def wrapper(src, includes: str, body: list, extra_sig: list, threads: int, min_blocks: int = 1) -> str:
@@ -228,7 +228,8 @@ def match_attention(src, strict: bool) -> Plan:
 
     nq = 2 if S % 256 == 0 else 1
     bh = math.prod(a.extent.as_static() for a in lead) if lead else 1
-    grid = bh * (S // (nq * 128))
+    items = bh * (S // (nq * 128))
+    grid = min(TARGET_SMS, items)
     threads = 64 + 128 * nq
     smem = (nq + 4) * 32768 + 1024 + 256
     scale_log2 = scale * math.log2(math.e)
@@ -241,8 +242,9 @@ def match_attention(src, strict: bool) -> Plan:
     extra = [tmap("q", ql.input, dt, (D, rows), (D * 2,), (64, 128)), tmap("k", kl.input, dt, (D, rows), (D * 2,), (64, 128)),
              tmap("v", vload.input, dt, (D, rows), (D * 2,), (64, 128)), dict(kind="status", name="status")]
     remarks = [f"attention template: {bh} (batch, head) pairs x {S} queries, head dimension 128, {dt}, "
-               f"{'causal' if causal else 'full'}; {grid} CTAs of {threads} threads, each {nq} query tile(s) of 128 rows "
-               "against 128-key tiles (TMA producer, tcgen05.mma issuer, one softmax warp group per query tile)",
+               f"{'causal' if causal else 'full'}; {grid} persistent CTAs of {threads} threads claim {items} work items of {nq} query "
+               "tile(s) of 128 rows against 128-key tiles (scheduler + TMA producer, tcgen05.mma issuer, one softmax warp group "
+               "per query tile); the next item's loads and first scores overlap the previous item's epilogue",
                "online softmax recognised (m, l, o with alpha = exp(m - max), beta = exp(s - max)); applied once per 128-key "
                "tile in base 2, O rescaled in tensor memory only when the maximum moves by more than 2^8",
                "S = Q K^T and O += P V on tcgen05.mma with S, P and O in tensor memory; K, V in two TMA stages each; "

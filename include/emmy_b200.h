@@ -47,7 +47,10 @@ enum { EMB_SWIZZLE_NONE = 0, EMB_SWIZZLE_32B = 1, EMB_SWIZZLE_64B = 2, EMB_SWIZZ
  * (emmy_ptx/ptx.py:294-295 .reqnctapercluster). `params[i]` points at the
  * i-th kernel parameter's value: an 8-byte device pointer for a buffer
  * (the reference's only parameter kind, `.param .u64 p_<buffer>`,
- * emmy_ptx/ptx.py:288), or a 128-byte tensor map made by emb_tensor_map. */
+ * emmy_ptx/ptx.py:288), or a 128-byte tensor map made by emb_tensor_map.
+ * A module's `status` parameter is a caller-owned buffer of 8 zeroed 32-bit
+ * words: [0..2] what a bounded wait that gave up recorded (code, CTA, step),
+ * [4..5] work counters a persistent kernel uses and re-zeroes itself. */
 typedef struct emb_launch_t {
     void* fn;
     uint32_t grid[3];
