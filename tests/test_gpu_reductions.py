@@ -17,7 +17,7 @@ from helpers import margin, oracle_problem, same_bits, source
 pytestmark = pytest.mark.gpu
 MODES = ("optimized", "strict", "plain")
 GOLDEN = [c for c in json.loads((Path(__file__).parent / "golden" / "oracle_cases.json").read_text())
-          if c["name"].startswith(("rand_cooperative", "rand_shared_reduction", "rand_attention", "self_max", "self_tree",
+          if c["name"].startswith(("rand_cooperative", "rand_shared_reduction", "rand_attention", "rand_pointwise", "self_",
                                    "wl_", "ex_r01", "ex_a01"))]
 
 
@@ -109,8 +109,9 @@ def test_golden_kernels_of_the_reference_interpreter(golden, case, mode):
     src = source("k_case", body, inputs, {k: np.zeros_like(v) for k, v in want.items()}, case["grid"], case["block"])
     got = runner.run_source(src, {**inputs, **{k: np.zeros_like(v) for k, v in want.items()}}, mode)
     uses_exp = "'exp'" in "".join(case["body"]) or "'erf'" in "".join(case["body"])
+    exact_family = name.startswith(("rand_pointwise", "self_integers"))  # typed arithmetic: every lowering must match exactly
     for k, w in want.items():
-        if mode == "strict" and not uses_exp:
+        if (mode == "strict" or exact_family) and not uses_exp:
             assert same_bits(got[k], w), (name, k)
         else:
             tol = 1e-4 if uses_exp else 1e-5
