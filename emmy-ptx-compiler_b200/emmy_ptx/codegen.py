@@ -32,7 +32,7 @@ from __future__ import annotations
 
 import math
 
-from . import ir
+from . import clusterize, ir
 from .ir import dtype_name, kind
 
 CTYPE = {"f32": "float", "f64": "double", "f16": "__half", "bf16": "__nv_bfloat16", "i8": "signed char",
@@ -109,6 +109,7 @@ class Emitter:
         self.guards = 0
         self.loop_depth = 0
         self.body = src.body
+        self.cluster = 1  # blocks per thread-block cluster the kernel asks for
 
     # ------------------------------------------------------------ text
 
@@ -335,7 +336,57 @@ class Emitter:
             inside = self.new_guard(self.conj(guard, f"(gid < {cells}LL)"))
             for axis in s.axes:  # masked threads keep zero
                 self.emit(f"if (!{inside}) v_{axis.name} = 0;")
-        self.block(s.body, inside if inside is not None else guard)
+        plan = None
+        if not self.plain and inside is None and guard is None and "clusters" not in getattr(self, "disable", ()):
+            plan = clusterize.plan(s, self.src.launch.grid, block)
+            if isinstance(plan, str):
+                if any(kind(t) in ("Loop", "StridedLoop") for t in s.body):
+                    self.remark(f"clusters: not used ({plan})")
+                plan = None
+        if plan is None:
+            self.block(s.body, inside if inside is not None else guard)
+        else:
+            self.clustered(plan, block)
+
+    def clustered(self, p, block: int) -> None:
+        """The Tile body with loop ``p.loop`` split over a cluster of 8: every block computes its eighth of
+        the iterations of the column-free part and stashes the results; after a cluster barrier every block
+        runs all iterations of its own part on values read from the owners' shared memory."""
+        self.cluster = clusterize.CLUSTER
+        nv, var = len(p.values), p.loop.axis.name
+        self.block(p.before, None)
+        self.emit("cooperative_groups::cluster_group emb_cluster = cooperative_groups::this_cluster();")
+        self.emit("const unsigned emb_rank = emb_cluster.block_rank();")
+        self.emit(f"__shared__ float emb_stash[{p.slots * block * nv}];")
+        start, _ = self.expr(p.start)
+        v = self.var(var, "i64")
+        self.seed(p.loop)
+        self.loop_depth += 1
+        self.emit(f"for (long long k_ = 0; k_ < {p.slots}LL; ++k_) {{")
+        self.depth += 1
+        self.emit(f"{v} = {start} + {p.step}LL * ((long long)emb_rank * {p.slots}LL + k_);")
+        self.block(p.shared, None)
+        for i, name in enumerate(p.values):
+            code, dt = self.use(name)
+            self.emit(f"emb_stash[(k_ * {block} + threadIdx.x) * {nv} + {i}] = {self.convert(code, dt, 'f32')};")
+        self.depth -= 1
+        self.emit("}")
+        self.emit("emb_cluster.sync();")
+        self.emit(f"for (long long j_ = 0; j_ < {p.trips}LL; ++j_) {{")
+        self.depth += 1
+        self.emit(f"{v} = {start} + {p.step}LL * j_;")
+        self.emit(f"const float* peer_ = emb_cluster.map_shared_rank(emb_stash, (unsigned)(j_ / {p.slots}LL));")
+        for i, name in enumerate(p.values):
+            self.emit(f"{self.var(name, 'f32')} = peer_[((j_ % {p.slots}LL) * {block} + threadIdx.x) * {nv} + {i}];")
+        self.block(p.own, None)
+        self.depth -= 1
+        self.emit("}")
+        self.loop_depth -= 1
+        self.emit("emb_cluster.sync();  // nobody leaves while a peer may still read its stash")
+        self.remark(f"clusters of {clusterize.CLUSTER}: the column-free part of the loop over {var} ({p.trips} iterations per thread) "
+                    f"is computed once per cluster, {p.slots} iterations per block, and {nv} value(s) per iteration pass through "
+                    f"distributed shared memory ({p.slots * block * nv * 4} B stash per block)")
+        self.block(p.after, None)
 
     def seed(self, loop) -> None:
         if not loop.seed:
@@ -667,7 +718,8 @@ def signature(src) -> str:
     return ", ".join(parts)
 
 
-PRELUDE = """#include "emb_ops.cuh"
+PRELUDE = """#include <cooperative_groups.h>
+#include "emb_ops.cuh"
 namespace emb {
 __device__ __forceinline__ long long trunc_div(long long a, long long b) { return b == 0 ? a : a / b; }
 __device__ __forceinline__ long long trunc_mod(long long a, long long b) { return b == 0 ? 0 : a % b; }
@@ -700,15 +752,17 @@ def pdl_prologue(src, enabled: bool) -> list:
     return out
 
 
-def generate(src, plain: bool = False, strict: bool = False) -> tuple:
-    """(CUDA source, remarks) of the statement-by-statement lowering of ``src``."""
+def generate(src, plain: bool = False, strict: bool = False, disable=()) -> tuple:
+    """(CUDA source, remarks, cluster size) of the statement-by-statement lowering of ``src``."""
     em = Emitter(src, plain, strict)
+    em.disable = frozenset(disable)
     em.block(src.body, None)
     decls = [f"    {CTYPE[dt]} v_{name} = emb::zero<{CTYPE[dt]}>();" for name, dt in em.vars.items() if name not in ("lane", "warp")]
     smem = [f"    __shared__ {CTYPE[dt]} s_{name}[{math.prod(shape)}];" for name, (dt, shape) in em.shared.items()]
+    attrs = f"__cluster_dims__({em.cluster}, 1, 1) " if em.cluster > 1 else ""
     head = [f"#define EMB_STRICT {int(strict)}", PRELUDE,
-            f'extern "C" __global__ void __launch_bounds__({src.launch.block}) {src.name}({signature(src)}) {{',
+            f'extern "C" __global__ void {attrs}__launch_bounds__({src.launch.block}) {src.name}({signature(src)}) {{',
             "    const unsigned emb_warp = __activemask();",
             "    int v_lane = threadIdx.x & 31, v_warp = threadIdx.x >> 5;",
             "    (void)emb_warp; (void)v_lane; (void)v_warp;"] + pdl_prologue(src, not plain)
-    return "\n".join(head + smem + decls + em.lines + ["}"]) + "\n", em.remarks
+    return "\n".join(head + smem + decls + em.lines + ["}"]) + "\n", em.remarks, em.cluster
