@@ -28,8 +28,8 @@ def test_plan_shape_for_the_shipped_example(tile):
 def test_refusals(tile):
     assert "threads outside the Tile" in clusterize.plan(tile, 4100, 8)
     assert isinstance(clusterize.plan(tile, 4096, 8), clusterize.ClusterPlan)
-    # a block of 16 threads holds two columns: no coordinate steps exactly one block
-    assert "no coordinate steps" in clusterize.plan(tile, 2048, 16)
+    # a block of 16 threads holds two columns of the 128: the column coordinate is neither inside a block nor across whole blocks
+    assert "straddles" in clusterize.plan(tile, 2048, 16)
     # a loop that is not pure (a Write inside) is left alone
     loop = next(s for s in tile.body if ir.kind(s) == "StridedLoop")
     w = ir.Write(output="matmul_1", index=(ir.Var(name="a0"), ir.Var(name="a1")), values=("v5",))
