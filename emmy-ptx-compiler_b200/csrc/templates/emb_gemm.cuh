@@ -58,12 +58,16 @@ template <int EPI> __device__ __forceinline__ float gemm_epilogue(float acc, flo
     return acc;
 }
 
-template <int STAGES, int GROUP_M, bool BF16, int EPI = EPI_NONE>
+// FP8: the operands are e4m3 byte codes (tcgen05 kind::f8f6f4, 128 elements per 128-byte row, K = 32 per MMA);
+// otherwise 16-bit (kind::f16, 64 elements per row, K = 16 per MMA). BF16 names the OUTPUT type (and, for the
+// 16-bit kind, the operand type).
+template <int STAGES, int GROUP_M, bool BF16, int EPI = EPI_NONE, bool FP8 = false>
 __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ map_a, const CUtensorMap* __restrict__ map_b,
                                                void* __restrict__ c_out, GemmShape shape, unsigned* status,
                                                const float* __restrict__ scale_ptr = nullptr) {
-    constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
-    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int ELEM = FP8 ? 1 : 2;                       // bytes per operand element
+    constexpr int BM = 128, BN = 256, BK = 128 / ELEM, UMMA_K = 32 / ELEM;  // a stage row and an MMA step are 128 and 32 bytes
+    constexpr uint32_t A_BYTES = BM * BK * ELEM, B_BYTES = BN * BK * ELEM, STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr uint32_t TMEM_COLS = 512;
     using out_t = typename Half16<BF16>::type;
 
@@ -136,7 +140,7 @@ __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ m
         }
     } else if (warp == 1) {
         if (tc::elect_one()) {
-            constexpr uint32_t idesc = tc::idesc_f16(BM, BN, BF16);
+            constexpr uint32_t idesc = FP8 ? tc::idesc_e4m3(BM, BN) : tc::idesc_f16(BM, BN, BF16);
             uint32_t it = 0, local = 0;
             bool alive = true;
             for (int t = blockIdx.x; alive && t < num_tiles; t += gridDim.x, ++local) {
@@ -154,9 +158,12 @@ __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ m
                     const uint8_t* stage = smem + s * STAGE_BYTES;
                     const uint64_t a_desc = tc::smem_desc_k128(stage), b_desc = tc::smem_desc_k128(stage + A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        tc::mma_f16_ss(d_tmem, a_desc + (k * UMMA_K * 2 >> 4), b_desc + (k * UMMA_K * 2 >> 4), idesc,
-                                       (kb | k) != 0);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        if (FP8)
+                            tc::mma_e4m3_ss(d_tmem, a_desc + (k * 32 >> 4), b_desc + (k * 32 >> 4), idesc, (kb | k) != 0);
+                        else
+                            tc::mma_f16_ss(d_tmem, a_desc + (k * 32 >> 4), b_desc + (k * 32 >> 4), idesc, (kb | k) != 0);
+                    }
                     tc::mma_commit(&empty[s]);  // the stage is free once these MMAs have read it
                 }
                 if (alive) tc::mma_commit(&tmem_full[buf]);

@@ -177,6 +177,34 @@ def matmul_f16(m: int = 8192, n: int = 8192, k: int = 8192, block: int = 256, dt
                          "b": dict(dtype=dtype, shape=[n, k], seed=1, dist="normal", scale=scale)})
 
 
+def matmul_fp8_body(m: int, n: int, k: int, block: int):
+    """C = (A . B^T) * scale with A [m, k] and B [n, k] e4m3 codes: decode, f32 products, f32 sum, one scale."""
+    loop = Loop(axis=Axis(name="a2", extent=k), body=(
+        Load(names=("c0",), input="a", index=(V("a0"), V("a2")), dtype=None),
+        Load(names=("c1",), input="b", index=(V("a1"), V("a2")), dtype=None),
+        Assign(name="w0", op="from_f8e4m3", args=("c0",), dtype=F32),
+        Assign(name="w1", op="from_f8e4m3", args=("c1",), dtype=F32),
+        Assign(name="v0", op="multiply", args=("w0", "w1"), dtype=F32),
+        Accum(name="acc0", value="v0", op="add", dtype=F32, axes=("a2",), base=None)), unroll=False, seed=True)
+    return (Tile(axes=(Axis(name="a0", extent=m), Axis(name="a1", extent=n)), body=(
+        Load(names=("s",), input="ab_scale", index=(I(0),), dtype=F32), loop,
+        Assign(name="y", op="multiply", args=("acc0", "s"), dtype=F32),
+        Write(output="matmul", index=(V("a0"), V("a1")), values=("y",), value_dtype=F32)), block_threads=block,
+        aux_threads=0, raster_axes=None, raster_group=None, raster_orient="m"),)
+
+
+def matmul_fp8(m: int = 8192, n: int = 8192, k: int = 8192, block: int = 256, ident: str = "m_e4m3_8192"):
+    """Both operands e4m3 (drawn from N(0, 1), per-tensor scaled), f32 accumulation, bf16 result."""
+    assert (m * n) % block == 0
+    kern = dict(node="matmul", entry="k_matmul_e4m3", body=matmul_fp8_body(m, n, k, block), grid=m * n // block, block=block,
+                inputs=["ab_scale", "a", "b"], output=("matmul", [m, n], "bf16"), final=True)
+    return dict(id=ident, code="(deq(a) @ deq(b).T) with e4m3 a, b", rtol=3e-2, atol=3e-2, graph_inputs=["a", "b"],
+                graph_outputs=["matmul"], kernels=[kern],
+                tensors={"a": dict(dtype="f8e4m3", shape=[m, k], seed=0, dist="normal", quant="a_scale"),
+                         "b": dict(dtype="f8e4m3", shape=[n, k], seed=1, dist="normal", quant="b_scale"),
+                         "ab_scale": dict(dtype="f32", shape=[1], scale_product=["a", "b"])})
+
+
 # ---------------------------------------------------------------- cfg 4: causal attention, online softmax
 
 
@@ -339,7 +367,7 @@ def _meta(problem: dict) -> dict:
             elif "data" in t:
                 args.append(dict(name=name, dtype=t["dtype"], shape=list(t["shape"]), data=list(t["data"])))
             else:  # ``seed`` as in the reference; dist/scale/quant/scale_of are this build's additions
-                extra = {k: t[k] for k in ("seed", "dist", "scale", "quant", "scale_of") if k in t}
+                extra = {k: t[k] for k in ("seed", "dist", "scale", "quant", "scale_of", "scale_product") if k in t}
                 args.append(dict(name=name, dtype=t["dtype"], shape=list(t["shape"]), **extra))
         oname, oshape, odtype = kern["output"]
         args.append(dict(name=oname, dtype=odtype, shape=list(oshape) or [1], output=True))

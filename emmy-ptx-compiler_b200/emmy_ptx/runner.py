@@ -58,7 +58,7 @@ def host_inputs(args: list) -> dict:
     """name -> numpy array for every argument that is neither an output nor an intermediate."""
     out, scales = {}, {}
     for a in args:
-        if a.get("output") or a.get("intermediate") or "scale_of" in a:
+        if a.get("output") or a.get("intermediate") or "scale_of" in a or "scale_product" in a:
             continue
         if "data" in a:
             out[a["name"]] = np.array(a["data"], numpy_dtype(a["dtype"])).reshape(a["shape"])
@@ -79,6 +79,8 @@ def host_inputs(args: list) -> dict:
     for a in args:
         if "scale_of" in a:
             out[a["name"]] = np.array([scales[a["scale_of"]]], np.float32)
+        elif "scale_product" in a:
+            out[a["name"]] = np.array([np.prod([np.float32(scales[n]) for n in a["scale_product"]], dtype=np.float32)], np.float32)
     return out
 
 

@@ -109,6 +109,60 @@ def match_matmul(src, strict: bool) -> Plan:
     return Plan("tensorcore", source, remarks, grid=grid, block=192, smem_bytes=smem, extra_params=extra)
 
 
+def match_matmul_e4m3(src, strict: bool) -> Plan:
+    """C = scale * A B^T with both operands e4m3 codes decoded by from_f8e4m3 (exact), f32 products and sum:
+    tcgen05 kind::f8f6f4 on the codes themselves, the scalar in the epilogue."""
+    tile = single_tile(src)
+    need(len(tile.axes) == 2, "the Tile is not over (row, column) cells")
+    m_axis, n_axis = tile.axes[0].name, tile.axes[1].name
+    M, N = tile.axes[0].extent.as_static(), tile.axes[1].extent.as_static()
+    body = list(tile.body)
+    need(len(body) == 4 and [kind(s) for s in body] == ["Load", "Loop", "Assign", "Write"], "the cell is not scale load, loop, scale, Write")
+    sl, loop, scale, write = body
+    sbuf = src.buffers.get(sl.input)
+    need(sbuf is not None and math.prod(sbuf.shape) == 1 and sbuf.dtype == "f32" and len(sl.names) == 1, "the leading Load is not an f32 scalar")
+    k_axis, K = loop.axis.name, loop.axis.extent.as_static()
+    need(loop.seed and [kind(s) for s in loop.body] == ["Load", "Load", "Assign", "Assign", "Assign", "Accum"],
+         "the loop is not Load, Load, decode, decode, multiply, Accum")
+    la, lb, da, db, mul, acc = loop.body
+    need({da.op.name, db.op.name} == {"from_f8e4m3"} and {da.args[0], db.args[0]} == {la.names[0], lb.names[0]}
+         and mul.op.name == "multiply" and set(mul.args) == {da.name, db.name} and dtype_name(mul.dtype) == "f32"
+         and acc.value == mul.name and acc.base is None and codegen.CANON.get(acc.op.name) == "add",
+         "the loop does not sum the f32 products of the two decoded codes")
+    def operand(load, axis):
+        return len(load.index) == 2 and is_var(load.index[0], axis) and is_var(load.index[1], k_axis)
+    if operand(la, m_axis) and operand(lb, n_axis):
+        a, b = la, lb
+    elif operand(lb, m_axis) and operand(la, n_axis):
+        a, b = lb, la
+    else:
+        raise Refusal("the operands are not A[row, k] and B[column, k]")
+    A, B, C = src.buffers.get(a.input), src.buffers.get(b.input), src.buffers.get(write.output)
+    need(A is not None and B is not None and C is not None and A.dtype == B.dtype == "f8e4m3" and C.dtype in ("bf16", "f16"),
+         "not e4m3 operands with a 16-bit result")
+    need(tuple(A.shape) == (M, K) and tuple(B.shape) == (N, K) and tuple(C.shape) == (M, N), "buffer shapes do not fit the cells")
+    need(scale.op.name == "multiply" and set(scale.args) == {acc.name, sl.names[0]} and tuple(write.values) == (scale.name,)
+         and len(write.index) == 2 and is_var(write.index[0], m_axis) and is_var(write.index[1], n_axis) and not write.atomic,
+         "the result is not the sum times the scalar, written at C[row, column]")
+    need(a.input not in src.written and b.input not in src.written, "the kernel writes an operand")
+    need(not strict, "the tensor cores sum a K-slice in their own order (--strict keeps the IR's)")
+    need(K % 16 == 0, "the row stride of the operands is not a multiple of 16 bytes (K % 16)")
+    tiles = math.ceil(M / 128) * math.ceil(N / 256)
+    grid = min(TARGET_SMS, tiles)
+    stage = (128 + 256) * 128
+    smem = GEMM_STAGES * stage + 1024 + 256
+    call = [f"    emb::gemm_tn_kernel<{GEMM_STAGES}, {GEMM_GROUP_M}, {str(C.dtype == 'bf16').lower()}, emb::EPI_SCALE, true>(&tmap_a, &tmap_b, "
+            f"p_{write.output}, emb::GemmShape{{{M}, {N}, {K}}}, status, p_{sl.input});"]
+    extra_sig = ["const __grid_constant__ CUtensorMap tmap_a", "const __grid_constant__ CUtensorMap tmap_b",
+                 "unsigned* __restrict__ status"]
+    source = wrapper(src, '#include "emb_gemm.cuh"', call, extra_sig, 192)
+    extra = [tmap("a", a.input, "u8", (K, M), (K,), (128, 128)), tmap("b", b.input, "u8", (K, N), (K,), (128, 256)),
+             dict(kind="status", name="status")]
+    remarks = [f"tensor-core matmul template, e4m3 operands: {M} x {N} x {K}, tcgen05 kind::f8f6f4 on the byte codes, f32 accumulation "
+               f"in tensor memory, the scalar in the epilogue; {tiles} tiles of 128 x 256 walked by {grid} persistent CTAs"]
+    return Plan("tensorcore", source, remarks, grid=grid, block=192, smem_bytes=smem, extra_params=extra)
+
+
 # ---------------------------------------------------------------- attention
 
 

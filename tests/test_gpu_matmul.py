@@ -73,3 +73,16 @@ def test_matmul_full_size_sampled_cells_and_properties():
     doubled = runner.Problem(folder, "optimized", inputs={"a": prob.host["a"] * np.float16(2), "b": prob.host["b"]}).run()["matmul"]
     normal = np.abs(got) >= np.float16(2.0 ** -13)
     assert normal.mean() > 0.9 and np.array_equal(doubled[normal], (got * np.float16(2))[normal])
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (256, 512, 384), (200, 264, 144)])
+def test_e4m3_matmul_against_the_oracle(tmp_path, m, n, k):
+    """Both operands e4m3 codes on tcgen05 kind::f8f6f4; the products are exact in f32 on both sides, only the order
+    of the sum and the bf16 rounding differ, so the result sits far inside the 3e-2 stated for fp8 data."""
+    block = 64 if (m * n) % 256 else 256
+    p = problems.matmul_fp8(m=m, n=n, k=k, block=block, ident="t")
+    prob = runner.Problem(problems.write(p, tmp_path), "optimized")
+    assert prob.kernels[0].launch_info["family"] == "tensorcore" and "f8f6f4" in prob.kernels[0].ptx
+    got = prob.run()["matmul"]
+    want = oracle_problem(p, prob.host)["matmul"]
+    check(got, want, "bf16")
