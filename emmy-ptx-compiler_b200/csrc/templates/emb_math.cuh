@@ -125,7 +125,7 @@ __device__ __forceinline__ float tanh_f32(float x) {
     float small = fmaf(x * s, p, x);
     float e = exp_f32(a + a);
     float big = copysignf(1.0f - 2.0f * __frcp_rn(e + 1.0f), x);
-    float r = a < 0.6f ? small : big;
+    float r = copysignf(a < 0.6f ? fabsf(small) : fabsf(big), x);  // tanh is odd: tanh(-0) = -0
     return x == x ? r : x;
 }
 
