@@ -1,10 +1,11 @@
-"""emmy_ptx for B200: a backend that compiles Emmy Kernel IR to PTX for sm_100a.
+"""emmy_ptx for B200: Emmy Kernel IR to PTX for sm_100a.
 
-Same entry points as the reference package (emmy_ptx/__init__.py:17-29)::
+The package keeps the reference's entry points (its emmy_ptx/__init__.py:17-29): ``compile_file``, ``load``,
+``Lowerer``, ``PTX_LIMIT``, ``PTX_VERSION``, ``TARGET``. Behind them::
 
-    frontend.load      IR json + meta.json           -> KernelSource
-    lower.Lowerer      kernel family or statements   -> Kernel (CUDA template instantiation, nvcc -ptx)
-    Kernel.render      nvcc's PTX                    -> the module text with the contract's header and parameters
+    frontend.load     *.ir.json + meta.json                    -> KernelSource      (ir.py reads the statements)
+    lower.Lowerer     a kernel-family template, or statements  -> Kernel            (CUDA C++ instantiation, nvcc -ptx)
+    Kernel.render     nvcc's PTX                               -> the module text   (header, launch line, p_<buffer> parameters)
 """
 
 from __future__ import annotations
@@ -16,52 +17,62 @@ from .frontend import load
 from .lower import Lowerer
 from .report import report as _report
 
-PTX_LIMIT = 2_000_000  # characters of PTX a runner accepts (emmy_ptx/ptx.py:35)
-PTX_VERSION = "8.8"  # CUDA 12.9's ISA: tcgen05, TMA and sm_100a
+PTX_LIMIT = 2_000_000     # characters of PTX a runner accepts (the reference's emmy_ptx/ptx.py:35)
+PTX_VERSION = "8.8"       # the ISA of CUDA 12.9: tcgen05, TMA, sm_100a
 TARGET = "sm_100a"
-EXPLORE_PTX_CHARS = 250_000  # emmy_ptx/__init__.py:24
+EXPLORE_PTX_CHARS = 250_000  # the module size --explore aims at (the reference's emmy_ptx/__init__.py:24)
+
+
+def _say(text: str) -> None:
+    print(text, file=sys.stderr)
+
+
+def _attempt(src, strict: bool, bulk_copy: bool, explore: bool):
+    """The optimizing lowering: (kernel, module text), or None after saying on stderr why it is not used."""
+    try:
+        kernel = Lowerer(src, strict=strict, bulk_copy=bulk_copy).run()
+        text = kernel.render(PTX_VERSION, TARGET)
+    except Exception:  # noqa: BLE001 - an IR shape a template or rewrite did not foresee must not cost the kernel its PTX
+        traceback.print_exc(file=sys.stderr)
+        return None
+    if explore and len(text) > EXPLORE_PTX_CHARS:
+        kernel.remarks.append(f"compile budget (--explore): target not met: {len(text)} characters remain, more than "
+                              f"{EXPLORE_PTX_CHARS} (the templates have no optional unrolling to give up)")
+    if len(text) > PTX_LIMIT:
+        _say(f"warning: {src.name}: {len(text)} characters of PTX, more than the runner accepts")
+        return None
+    return kernel, text
 
 
 def compile_file(ir_path: str, plain: bool = False, strict: bool = False, report: bool = False,
                  bulk_copy: bool = False, explore: bool = False) -> str:
-    """Compile one ``*.ir.json`` file and return the PTX module text.
+    """The PTX module text of one ``*.ir.json`` file.
 
-    The modes are the reference's (emmy_ptx/__init__.py:28-85). Optimized: a kernel
-    family's template where the pattern and the legality checks pass. ``strict``: only
-    what keeps every floating-point result bit for bit as the IR's own order and rounding
-    give it (for the reductions the template in its in-order form; no FMA contraction).
-    ``plain``: every statement by its own rule, nothing else. Should the optimized
-    lowering raise, or give more than PTX_LIMIT characters, the kernel is lowered again
-    plainly, with the traceback and a warning on stderr. ``report`` writes the decisions
-    and a PTX profile to stderr and changes no PTX. ``bulk_copy`` is accepted and changes
-    nothing: the tensor-core templates always load through the TMA unit. ``explore`` is
-    accepted: the templates are rolled loops, there is no unrolling to scale down, and the
-    report says so when the size target is missed."""
+    Modes as in the reference (its emmy_ptx/__init__.py:28-85). By default a kernel family's template is used
+    where its pattern and legality checks pass. ``strict`` keeps only what leaves every floating-point result bit
+    for bit as the IR's order and rounding give it. ``plain`` lowers statement by statement and nothing else. If
+    the default lowering raises, or its module is longer than PTX_LIMIT, the traceback or a warning goes to
+    stderr and the kernel is lowered plainly instead (a safety net for the lowering, not a check of its code).
+    ``report`` prints decisions and a PTX profile on stderr without changing the PTX. ``bulk_copy`` and
+    ``explore`` are accepted: TMA loads are always on in the tensor-core templates, and there is no optional
+    unrolling whose budget could be scaled (the report says so when the size target is missed).
+    """
     src = load(ir_path)
-    mode = "strictly" if strict else "optimized"
-    if not plain:
-        try:
-            kernel = Lowerer(src, strict=strict, bulk_copy=bulk_copy).run()
-            ptx = kernel.render(PTX_VERSION, TARGET)
-            if explore and len(ptx) > EXPLORE_PTX_CHARS:
-                kernel.remarks.append(f"compile budget (--explore): target not met: {len(ptx)} characters remain, more than "
-                                      f"{EXPLORE_PTX_CHARS} (the templates have no optional unrolling to give up)")
-            if len(ptx) <= PTX_LIMIT:
-                if report:
-                    print(_report(src, kernel, ptx, mode), file=sys.stderr)
-                return ptx
-            print(f"warning: {src.name}: {len(ptx)} characters of PTX, more than the runner accepts", file=sys.stderr)
-        except Exception:  # noqa: BLE001 - whatever failed, the plain lowering may still succeed
-            traceback.print_exc(file=sys.stderr)
-        print(f"warning: {src.name}: lowering it again without the optional rewrites", file=sys.stderr)
-        mode = "plainly (the fallback)"
+    if plain:
+        how = "plainly and strictly" if strict else "plainly"
     else:
-        mode = "plainly" + (" and strictly" if strict else "")
+        done = _attempt(src, strict, bulk_copy, explore)
+        if done is not None:
+            kernel, text = done
+            if report:
+                _say(_report(src, kernel, text, "strictly" if strict else "optimized"))
+            return text
+        _say(f"warning: {src.name}: lowering it again without the optional rewrites")
+        how = "plainly (the fallback)"
     kernel = Lowerer(src, plain=True, strict=strict).run()
-    ptx = kernel.render(PTX_VERSION, TARGET)
-    if len(ptx) > PTX_LIMIT:
-        print(f"error: {src.name}: even the plain lowering gives {len(ptx)} characters of PTX, more than the "
-              f"runner's {PTX_LIMIT}", file=sys.stderr)
+    text = kernel.render(PTX_VERSION, TARGET)
+    if len(text) > PTX_LIMIT:
+        _say(f"error: {src.name}: even the plain lowering gives {len(text)} characters of PTX, more than the runner's {PTX_LIMIT}")
     if report:
-        print(_report(src, kernel, ptx, mode), file=sys.stderr)
-    return ptx
+        _say(_report(src, kernel, text, how))
+    return text

@@ -1,18 +1,21 @@
-"""``compile.py --report``: what the lowering decided for a kernel, and a static profile of its PTX.
+"""``compile.py --report``: the lowering's decisions for one kernel and a static census of its PTX, on stderr.
 
-The output contract is the reference's (emmy_ptx/report.py:76-87): first line
-``<entry>: <n> block(s) x <threads> threads[, N B of dynamic shared memory]; lowered <mode>``,
-then every remark once (with its count when repeated), last ``  PTX: <n> instructions: ...`` by
-kind. The kinds counted here are the ones that matter on sm_100a: tensor-core (tcgen05) and
-tensor-memory instructions, TMA copies and mbarrier operations next to the classic ones.
+Output contract (the reference's emmy_ptx/report.py:76-87, checked by its tests/test_compile.py:83-98):
+
+    <entry>: <n> block(s) x <threads> threads[, <bytes> B of dynamic shared memory]; lowered <mode>
+      <remark>                      one line per distinct remark, in order of first appearance, "(xN)" when repeated
+      PTX: <count> instructions: <count> <kind>, ...
+
+The census counts what matters on sm_100a: tensor-core (tcgen05) and tensor-memory instructions, TMA copies and
+mbarrier operations, warp reductions, next to loads, stores, float arithmetic, special functions and branches.
 """
 
 from __future__ import annotations
 
 import re
-from collections import Counter
 
-KINDS = (
+# (label for one, label for several, pattern the opcode must start with), in print order; first match wins
+CENSUS = [
     ("FMA", "FMAs", r"fma\.\S*f(16|32|64)"),
     ("other float op", "other float ops", r"(add|sub|mul|div|max|min|neg|abs|cvt)\.\S*(f16|bf16|f32|f64)"),
     ("special function", "special functions", r"(ex2|lg2|rcp|sqrt|rsqrt|sin|cos|tanh)\."),
@@ -29,44 +32,45 @@ KINDS = (
     ("warp reduction", "warp reductions", r"redux\."),
     ("barrier", "barriers", r"(bar|barrier)\."),
     ("branch", "branches", r"bra\b"),
-)
+]
+_NOT_CODE = ("//", ".", "{", "}", "$", "(", ")")
 
 
-def instruction_lines(ptx: str):
-    for line in ptx.splitlines():
-        text = line.strip()
-        if not text or text.startswith(("//", ".", "{", "}", "$", "(", ")")) or text.endswith(":"):
-            continue
-        yield re.sub(r"^@!?%p\d+\s+", "", text)
+def opcodes(ptx: str):
+    """The opcode of every instruction line of a module (directives, labels, braces and comments skipped)."""
+    for raw in ptx.splitlines():
+        line = raw.strip()
+        if line and not line.startswith(_NOT_CODE) and not line.endswith(":"):
+            yield re.sub(r"^@!?%p\d+\s+", "", line).split(None, 1)[0]
 
 
 def profile(ptx: str) -> str:
-    counts, vectors, total = Counter(), Counter(), 0
-    for text in instruction_lines(ptx):
+    tally = {one: [0, 0] for one, _, _ in CENSUS}  # label -> [count, of which vector accesses]
+    total = 0
+    for op in opcodes(ptx):
         total += 1
-        op = text.split(None, 1)[0]
-        for one, _, pattern in KINDS:
-            if re.match(pattern, op):
-                counts[one] += 1
-                if ".v2." in op or ".v4." in op or ".v8." in op:
-                    vectors[one] += 1
-                break
-    parts = []
-    for one, many, _ in KINDS:
-        if counts[one]:
-            vec = f" ({vectors[one]} vector)" if vectors[one] else ""
-            parts.append(f"{counts[one]} {one if counts[one] == 1 else many}{vec}")
-    return f"{total} instructions: " + ", ".join(parts)
+        hit = next((one for one, _, pattern in CENSUS if re.match(pattern, op)), None)
+        if hit is not None:
+            tally[hit][0] += 1
+            tally[hit][1] += bool(re.search(r"\.v[248]\.", op))
+    shown = []
+    for one, several, _ in CENSUS:
+        count, vectors = tally[one]
+        if count:
+            shown.append(f"{count} {one if count == 1 else several}" + (f" ({vectors} vector)" if vectors else ""))
+    return f"{total} instructions: " + ", ".join(shown)
 
 
 def report(src, kernel, ptx: str, mode: str) -> str:
-    launch = kernel.launch
-    grid, block, smem = launch["grid"][0], launch["block"][0], launch["smem_bytes"]
-    blocks = "1 block" if grid == 1 else f"{grid} blocks"
-    dyn = f", {smem} B of dynamic shared memory" if smem else ""
-    out = [f"{kernel.name}: {blocks} x {block} threads{dyn}; lowered {mode}"]
-    counts = Counter(kernel.remarks)
-    for text in dict.fromkeys(kernel.remarks):
-        out.append(f"  {text}" + (f"  (x{counts[text]})" if counts[text] > 1 else ""))
-    out.append(f"  PTX: {profile(ptx)}")
-    return "\n".join(out)
+    shape = kernel.launch
+    blocks, threads, dynamic = shape["grid"][0], shape["block"][0], shape["smem_bytes"]
+    first = f"{kernel.name}: {'1 block' if blocks == 1 else f'{blocks} blocks'} x {threads} threads"
+    if dynamic:
+        first += f", {dynamic} B of dynamic shared memory"
+    lines = [first + f"; lowered {mode}"]
+    seen = {}
+    for remark in kernel.remarks:
+        seen[remark] = seen.get(remark, 0) + 1
+    lines += [f"  {remark}" + (f"  (x{n})" if n > 1 else "") for remark, n in seen.items()]
+    lines.append(f"  PTX: {profile(ptx)}")
+    return "\n".join(lines)

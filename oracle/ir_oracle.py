@@ -488,36 +488,38 @@ def _decode_e4m3(t, code):
     return byte.view(ml_dtypes.float8_e4m3fn).astype(np.float32).astype(t)
 
 
-_UNARY = {
-    "negative": lambda t, x: np.negative(x.astype(t)),
-    "abs": lambda t, x: np.abs(x.astype(t)),
-    "copy": lambda t, x: x.astype(t),
-    "pad": lambda t, x: x.astype(t),
-    "square": lambda t, x: np.multiply(x.astype(t), x.astype(t)),
-    "reciprocal": lambda t, x: np.divide(t(1), x.astype(t)),
-    "relu": lambda t, x: fmax(x.astype(t), t(0)),
-    "sqrt": lambda t, x: np.sqrt(x.astype(t)),
-    "exp": _in_double(np.exp),
-    "log": _in_double(np.log),
-    "tanh": _in_double(np.tanh),
-    "sin": _in_double(np.sin),
-    "cos": _in_double(np.cos),
-    "erf": _in_double(_erf),
-    "sigmoid": _in_double(lambda x: 1 / (1 + np.exp(-x))),
-    "rsqrt": _in_double(lambda x: 1 / np.sqrt(x)),
-    "bitwise_count": lambda t, x: np.bitwise_count(x).astype(t),
-    "from_f8e4m3": _decode_e4m3,
-}
-_BINARY = {
-    "add": np.add, "subtract": np.subtract, "multiply": np.multiply, "divide": np.divide, "maximum": fmax,
-    "minimum": fmin, "floor_divide": np.floor_divide, "remainder": np.remainder, "mod": np.remainder,
-    "left_shift": np.left_shift, "right_shift": np.right_shift, "bitwise_and": np.bitwise_and,
-    "bitwise_or": np.bitwise_or, "bitwise_xor": np.bitwise_xor,
-}
-_INTEGER_ONLY = frozenset({"floor_divide", "remainder", "mod", "left_shift", "right_shift", "bitwise_xor",
-                           "bitwise_count"})
-_COMPARE = {"equal": np.equal, "not_equal": np.not_equal, "greater": np.greater, "less": np.less,
-            "greater_equal": np.greater_equal, "less_equal": np.less_equal}
+def _cast_then(fn):
+    """A unary computed in the result type: convert the operand first, then apply ``fn``."""
+    return lambda t, x: fn(x.astype(t), t)
+
+
+# one-operand operations (tests/oracle.py:310-322): arithmetic ones in the result type, transcendental ones in double
+_UNARY = {name: _cast_then(fn) for name, fn in {
+    "negative": lambda v, t: np.negative(v),
+    "abs": lambda v, t: np.abs(v),
+    "copy": lambda v, t: v,
+    "pad": lambda v, t: v,
+    "square": lambda v, t: np.multiply(v, v),
+    "reciprocal": lambda v, t: np.divide(t(1), v),
+    "relu": lambda v, t: fmax(v, t(0)),
+    "sqrt": lambda v, t: np.sqrt(v),
+}.items()}
+_UNARY.update({name: _in_double(fn) for name, fn in {
+    "exp": np.exp, "log": np.log, "tanh": np.tanh, "sin": np.sin, "cos": np.cos, "erf": _erf,
+    "sigmoid": lambda x: 1 / (1 + np.exp(-x)), "rsqrt": lambda x: 1 / np.sqrt(x),
+}.items()})
+_UNARY["bitwise_count"] = lambda t, x: np.bitwise_count(x).astype(t)
+_UNARY["from_f8e4m3"] = _decode_e4m3  # extension
+
+# two-operand operations (tests/oracle.py:323-328), computed on operands converted to the result type
+_BINARY = dict(add=np.add, subtract=np.subtract, multiply=np.multiply, divide=np.divide, maximum=fmax, minimum=fmin,
+               floor_divide=np.floor_divide, remainder=np.remainder, mod=np.remainder, left_shift=np.left_shift,
+               right_shift=np.right_shift, bitwise_and=np.bitwise_and, bitwise_or=np.bitwise_or, bitwise_xor=np.bitwise_xor)
+# operations emmy renders on integers only: for a bool result they are computed in i32, all others in f32 (:329-330)
+_INTEGER_ONLY = frozenset("floor_divide remainder mod left_shift right_shift bitwise_xor bitwise_count".split())
+# comparisons happen in the operands' common type; the result is the test's 0 or 1 (:331-332)
+_COMPARE = dict(equal=np.equal, not_equal=np.not_equal, greater=np.greater, less=np.less, greater_equal=np.greater_equal,
+                less_equal=np.less_equal)
 
 
 def apply(op: str, args: list, out: str):
