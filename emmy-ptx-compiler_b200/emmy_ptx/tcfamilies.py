@@ -42,7 +42,26 @@ def wrapper(src, includes: str, body: list, extra_sig: list, threads: int, min_b
     return "\n".join(head + codegen.pdl_prologue(src, True) + body + ["}"]) + "\n"
 
 
-def tmap(name: str, buffer: str, dtype: str, dims, strides_bytes, box, swizzle: str = "128B") -> dict:
+ELEMENT_BYTES = {"u8": 1, "f8e4m3": 1, "f16": 2, "bf16": 2, "f32": 4}
+SWIZZLE_SPAN = {"none": None, "32B": 32, "64B": 64, "128B": 128}
+
+
+def tmap(name: str, buffer: str, dtype: str, dims, strides_bytes, box, swizzle: str = "128B", step=None) -> dict:
+    """A tensor-map parameter for the launch header, proved usable on the host before any kernel runs: the
+    role the reference's bulk-copy planner has for its copy-engine fills (emmy_ptx/bulk.py:34-57,138-148: it
+    evaluates every address and only hands over runs that are contiguous and 16-byte aligned). What a TMA tile
+    copy needs: row strides that are multiples of 16 bytes, a box of at most 256 per dimension whose inner extent
+    is the swizzle span, and - the one rule nothing checks at run time - inner coordinates that are multiples of
+    16 bytes; the templates only ever ask for coordinates that are multiples of ``step`` (default: the box)."""
+    size = ELEMENT_BYTES[dtype]
+    step = list(step) if step is not None else list(box)
+    need(all(int(s) % 16 == 0 for s in strides_bytes), f"tensor map {name}: a row stride is not a multiple of 16 bytes")
+    need(all(1 <= int(b) <= 256 for b in box), f"tensor map {name}: a box extent is outside 1..256")
+    need((int(box[0]) * size) % 16 == 0, f"tensor map {name}: the inner box extent is not a multiple of 16 bytes")
+    span = SWIZZLE_SPAN[swizzle]
+    need(span is None or int(box[0]) * size == span, f"tensor map {name}: the inner box extent is not the {swizzle} swizzle span")
+    need((int(step[0]) * size) % 16 == 0, f"tensor map {name}: the template's inner coordinates are not multiples of 16 bytes")
+    need(all(int(d) >= 1 for d in dims) and len(dims) == len(box) == len(strides_bytes) + 1, f"tensor map {name}: rank mismatch")
     return dict(kind="tmap", name=name, buffer=buffer, dtype=dtype, dims=[int(d) for d in dims],
                 strides_bytes=[int(s) for s in strides_bytes], box=[int(b) for b in box], swizzle=swizzle)
 

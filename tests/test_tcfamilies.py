@@ -96,3 +96,16 @@ def test_mlp_is_taken_with_its_chain_and_refused(tmp_path):
                                   {**src.constants, "gelu_k": 0.05}, src.meta)
     with pytest.raises(families.Refusal, match="constants or wiring"):
         tcfamilies.match_mlp(wrong, False)
+
+
+def test_tensor_maps_are_proved_on_the_host():
+    """Row strides, box extents and the inner coordinates a template will ask for are checked before anything runs
+    (an inner coordinate that is not a multiple of 16 bytes is an illegal instruction at run time)."""
+    ok = tcfamilies.tmap("a", "a", "f16", (4096, 128), (8192,), (64, 128))
+    assert ok["box"] == [64, 128] and ok["swizzle"] == "128B"
+    for bad, why in ((dict(strides_bytes=(8190,)), "row stride"), (dict(box=(64, 512)), "outside 1..256"),
+                     (dict(box=(32, 128)), "swizzle span"), (dict(step=(4, 128)), "coordinates")):
+        args = dict(name="a", buffer="a", dtype="f16", dims=(4096, 128), strides_bytes=(8192,), box=(64, 128))
+        args.update(bad)
+        with pytest.raises(families.Refusal, match=why):
+            tcfamilies.tmap(**args)
