@@ -202,7 +202,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--buffer-sets", type=int, default=0, help="copies of every buffer the passes rotate through (0: enough "
                     "to exceed L2; 1 keeps device memory small for a profiler capture)")
-    ap.add_argument("--families", default="sum,matmul,attention,mlp", help="comma-separated extra workloads measured after the headline one")
+    ap.add_argument("--families", default=None, help="comma-separated extra workloads measured after the headline one "
+                    "(default: all of them on one GPU, the array sum with its exchange on several)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -213,6 +214,8 @@ def main() -> None:
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.families is None:
+        args.families = "sum,matmul,attention,mlp" if world == 1 else "sum"
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the kernels run on the GPU only")
     torch.cuda.set_device(local)
