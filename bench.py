@@ -289,15 +289,21 @@ def main() -> None:
             d2h = sum(t.numel() * t.element_size() for t in out_host.values())
             reps = max(3, min(steps, 10))
             times = []
+            # rows are independent in this workload's kernel: the public API pipelines slices of rows (copy in, launch,
+            # copy out on a few streams) so that both directions of the host link and the GPU work at once
+            pipelined = prob.rows_pipeline(chunks=8, streams=4)
             barrier()
             for i in range(2 + reps):
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record()
-                for n, t in pinned.items():
-                    ins[n].copy_(t, non_blocking=True)
-                driver.launch(prob.launches, stream)
-                for n in outs:
-                    out_host[n].copy_(prob.tensors[n], non_blocking=True)
+                if pipelined is not None:
+                    pipelined(pinned, out_host)
+                else:
+                    for n, t in pinned.items():
+                        ins[n].copy_(t, non_blocking=True)
+                    driver.launch(prob.launches, stream)
+                    for n in outs:
+                        out_host[n].copy_(prob.tensors[n], non_blocking=True)
                 b.record()
                 b.synchronize()
                 if i >= 2:
@@ -306,7 +312,9 @@ def main() -> None:
             t_e2e = torch.tensor([statistics.mean(times)], dtype=torch.float64, device="cuda")
             if world > 1:
                 dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
-            e2e = dict(value=float(t_e2e.item()), unit="us", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h)
+            e2e = dict(value=float(t_e2e.item()), unit="us", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
+                       how="8 row slices on 4 streams: copy in, launch, copy out overlap" if pipelined is not None else
+                           "copy in, launches, copy out on one stream")
         return prob, mean_us, timing, roof, e2e
 
     sampler = ClockSampler(local)

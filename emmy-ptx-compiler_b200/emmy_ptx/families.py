@@ -54,6 +54,7 @@ class Plan:
     extra_params: list = field(default_factory=list)  # tensor maps and scratch the launch header lists
     nvcc_flags: tuple = ()
     pre: list = field(default_factory=list)  # launches of auxiliary entries of the same module, run before the main one
+    rows: dict | None = None  # row independence: {"count": R, "buffers": {name: bytes per row}}, one CTA per row
 
 
 def need(cond, why: str) -> None:
@@ -393,7 +394,9 @@ def match_softmax(src, strict: bool) -> Plan:
                "row maximum: " + ("butterfly and tree in the IR's order" if strict else "redux.sync.max per warp, then the tree"),
                "row sum: butterfly over 32 lanes, then the tree's order behind one barrier"]
     del out_pointer
-    return Plan("softmax", source, remarks)
+    lead_rows = math.prod(src.buffers[ld1.input].shape[:-1])
+    independent = dict(count=lead_rows, buffers={ld1.input: cols * 4, w.output: cols * 4}) if lead_rows == src.launch.grid else None
+    return Plan("softmax", source, remarks, rows=independent)
 
 
 MATCHERS = (("softmax", match_softmax), ("reduce", match_reduce))

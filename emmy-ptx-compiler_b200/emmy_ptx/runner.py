@@ -253,6 +253,51 @@ class Problem:
         self.check_status()
         return out
 
+    def rows_pipeline(self, chunks: int = 4, streams: int = 3):
+        """For a one-kernel problem whose launch header declares its rows independent (one CTA per row of the listed
+        buffers): a callable ``run(host_in, host_out)`` that processes the rows in ``chunks`` slices, each slice's
+        host-to-device copy, launch and device-to-host copy on one of ``streams`` CUDA streams, so that the copies of
+        one slice overlap the compute and the opposite-direction copies of its neighbours. ``host_in`` / ``host_out``
+        map buffer names to pinned host tensors of the full shapes. Returns None when the kernel declares no such rows."""
+        import torch
+        if len(self.kernels) != 1 or len(self.launches) != 1:
+            return None
+        k = self.kernels[0]
+        info = k.launch_info.get("rows")
+        if not info or any(p["kind"] != "buffer" for p in k.launch_info["params"]):
+            return None
+        total = info["count"]
+        bounds = [total * c // chunks for c in range(chunks + 1)]
+        pool = [torch.cuda.Stream(self.device) for _ in range(streams)]
+        li = k.launch_info
+        pieces = []
+        for c in range(chunks):
+            lo, hi = bounds[c], bounds[c + 1]
+            if hi == lo:
+                continue
+            params = [self.tensors[p["name"]].data_ptr() + lo * info["buffers"].get(p["name"], 0) for p in li["params"]]
+            pieces.append((lo, hi, driver.Launch(k.function, [hi - lo, 1, 1], li["block"], li.get("cluster", 1),
+                                                 li.get("smem_bytes", 0), params)))
+        ins = [n for n in info["buffers"] if n in self.host]
+        outs = [n for n in info["buffers"] if n not in self.host]
+
+        def run(host_in: dict, host_out: dict) -> None:
+            main = torch.cuda.current_stream(self.device)
+            start = torch.cuda.Event()
+            start.record(main)
+            for idx, (lo, hi, launch) in enumerate(pieces):
+                s = pool[idx % len(pool)]
+                s.wait_event(start)
+                with torch.cuda.stream(s):
+                    for n in ins:
+                        self.tensors[n][lo:hi].copy_(host_in[n][lo:hi], non_blocking=True)
+                    driver.launch([launch], s.cuda_stream)
+                    for n in outs:
+                        host_out[n][lo:hi].copy_(self.tensors[n][lo:hi], non_blocking=True)
+            for s in pool:
+                main.wait_stream(s)
+        return run
+
     def launch_count(self) -> int:
         return len(self.launches)
 

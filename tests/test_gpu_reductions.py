@@ -119,3 +119,21 @@ def test_golden_kernels_of_the_reference_interpreter(golden, case, mode):
             if w.dtype == np.float16:
                 tol = 2e-3
             assert np.allclose(g, w64, rtol=tol, atol=tol / 10 * max(1.0, float(np.abs(w64).max()))), (name, k)
+
+
+def test_rows_pipeline_gives_the_same_softmax(tmp_path):
+    """Slices of rows copied in, computed and copied out on several streams: the same bits as one launch."""
+    import torch
+    p = problems.row_softmax(rows=96, cols=1024, block=64, ident="t")
+    prob = runner.Problem(problems.write(p, tmp_path), "optimized")
+    whole = prob.run()["softmax"]
+    run = prob.rows_pipeline(chunks=5, streams=3)
+    assert run is not None
+    x = torch.from_numpy(prob.host["x"]).pin_memory()
+    out = torch.zeros(96, 1024).pin_memory()
+    prob.tensors["softmax"].zero_()
+    run({"x": x}, {"softmax": out})
+    torch.cuda.synchronize()
+    assert same_bits(out.numpy(), whole)
+    assert runner.Problem(problems.write(problems.array_sum(n=4096, grid=4, block=128, final_block=64, ident="s"), tmp_path),
+                          "optimized").rows_pipeline() is None
