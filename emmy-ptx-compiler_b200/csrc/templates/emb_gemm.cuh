@@ -230,4 +230,188 @@ __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ m
     }
 }
 
+// The same matmul on CTA PAIRS: a cluster of two CTAs (the two SMs of a TPC) owns a 256 x 256 output tile and
+// runs it as ONE tcgen05.mma.cta_group::2 of 256 x 256 x 16 per step. CTA r of the pair loads rows
+// 128 r .. 128 r + 127 of the tile's A panel and of its B panel (half of what a lone CTA would load for the same
+// amount of tensor work, so a stage is 32 KB and the ring can be deeper) and holds lanes = rows 128 r .. of
+// the accumulator in its own tensor memory. Roles per CTA as above, with these differences:
+//
+//   producer  both CTAs load their halves; the bytes of both are counted on the LEADER's (rank 0) full barrier
+//   MMA       only the leader issues; its commits arrive on the empty / accumulator-full barriers of BOTH CTAs
+//   epilogue  both CTAs drain their own 128 lanes; every epilogue warp of both arrives on the leader's
+//             accumulator-empty barrier (8 arrivals)
+//
+// The tensor maps must have boxes of 128 rows for A and for B.
+template <int STAGES, int GROUP_M, bool BF16, int EPI = EPI_NONE, bool FP8 = false>
+__device__ __forceinline__ void gemm_tn_pair_kernel(const CUtensorMap* __restrict__ map_a, const CUtensorMap* __restrict__ map_b,
+                                                    void* __restrict__ c_out, GemmShape shape, unsigned* status,
+                                                    const float* __restrict__ scale_ptr = nullptr) {
+    constexpr int ELEM = FP8 ? 1 : 2;
+    constexpr int BM = 256, BN = 256, HALF = 128, BK = 128 / ELEM, UMMA_K = 32 / ELEM;
+    constexpr uint32_t A_BYTES = HALF * BK * ELEM, B_BYTES = HALF * BK * ELEM, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t TMEM_COLS = 512;
+    using out_t = typename Half16<BF16>::type;
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // the same offsets in both CTAs: the MMA applies one descriptor to both shared memories
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* full = bars;                    // used in the leader only
+    uint64_t* empty = bars + STAGES;          // one set per CTA
+    uint64_t* tmem_full = bars + 2 * STAGES;  // one set per CTA
+    uint64_t* tmem_empty = bars + 2 * STAGES + 2;  // used in the leader only
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+    const tc::Guard guard{status, abort_flag};
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = tc::cluster_ctarank();
+    const int pair = tc::cluster_id_x(), pairs = tc::cluster_count_x();
+    const int tiles_m = (shape.m + BM - 1) / BM, tiles_n = (shape.n + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int k_blocks = (shape.k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            tc::mbar_init(&full[s], 1);
+            tc::mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            tc::mbar_init(&tmem_full[b], 1);
+            tc::mbar_init(&tmem_empty[b], 8);  // one arrival per epilogue warp of both CTAs
+        }
+        *abort_flag = 0;
+        tc::mbar_init_fence();
+        tc::tma_prefetch_desc(map_a);
+        tc::tma_prefetch_desc(map_b);
+    }
+    if (warp == 1) tc::tmem_alloc_pair(tmem_holder, TMEM_COLS);
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::cluster_sync();  // the peer's barriers exist before anything arrives on them
+    tc::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_holder;
+
+    auto tile_coords = [&](int t, int& tm, int& tn) {
+        const int per_group = GROUP_M * tiles_n;
+        const int g = t / per_group, r = t % per_group;
+        const int rows = min(GROUP_M, tiles_m - g * GROUP_M);
+        tm = g * GROUP_M + r % rows;
+        tn = r / rows;
+    };
+
+    if (warp == 0) {
+        if (tc::elect_one()) {
+            uint32_t it = 0;
+            bool alive = true;
+            for (int t = pair; alive && t < num_tiles; t += pairs) {
+                int tm, tn;
+                tile_coords(t, tm, tn);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                    if (!tc::mbar_wait(&empty[s], ph ^ 1, guard, tc::WAIT_SMEM_EMPTY, it)) {
+                        alive = false;
+                        break;
+                    }
+                    if (rank == 0) tc::mbar_arrive_expect_tx(&full[s], 2 * STAGE_BYTES);
+                    const uint32_t leader_full = tc::smem_of_cta(&full[s], 0);
+                    uint8_t* stage = smem + s * STAGE_BYTES;
+                    tc::tma_load_2d_pair(stage, map_a, leader_full, kb * BK, tm * BM + rank * HALF);
+                    tc::tma_load_2d_pair(stage + A_BYTES, map_b, leader_full, kb * BK, tn * BN + rank * HALF);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (rank == 0 && tc::elect_one()) {
+            constexpr uint32_t idesc = FP8 ? tc::idesc_e4m3(BM, BN) : tc::idesc_f16(BM, BN, BF16);
+            uint32_t it = 0, local = 0;
+            bool alive = true;
+            for (int t = pair; alive && t < num_tiles; t += pairs, ++local) {
+                const uint32_t buf = local & 1, use = local >> 1;
+                if (!tc::mbar_wait(&tmem_empty[buf], (use & 1) ^ 1, guard, tc::WAIT_TMEM_EMPTY, local)) break;
+                tc::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                    if (!tc::mbar_wait(&full[s], ph, guard, tc::WAIT_SMEM_FULL, it)) {
+                        alive = false;
+                        break;
+                    }
+                    tc::tc_fence_after_sync();
+                    const uint8_t* stage = smem + s * STAGE_BYTES;
+                    const uint64_t a_desc = tc::smem_desc_k128(stage), b_desc = tc::smem_desc_k128(stage + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        if (FP8)
+                            tc::mma_e4m3_ss_pair(d_tmem, a_desc + (k * 32 >> 4), b_desc + (k * 32 >> 4), idesc, (kb | k) != 0);
+                        else
+                            tc::mma_f16_ss_pair(d_tmem, a_desc + (k * 32 >> 4), b_desc + (k * 32 >> 4), idesc, (kb | k) != 0);
+                    }
+                    tc::mma_commit_pair(&empty[s], 3);  // the stage is free in both CTAs once these MMAs have read it
+                }
+                if (alive) tc::mma_commit_pair(&tmem_full[buf], 3);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        uint32_t local = 0;
+        out_t* c = static_cast<out_t*>(c_out);
+        const bool vec_ok = (shape.n % 8) == 0;
+        const float scale = (EPI != EPI_NONE && scale_ptr) ? __ldg(scale_ptr) : 1.0f;
+        for (int t = pair; t < num_tiles; t += pairs, ++local) {
+            int tm, tn;
+            tile_coords(t, tm, tn);
+            const uint32_t buf = local & 1, use = local >> 1;
+            if (!tc::mbar_wait(&tmem_full[buf], use & 1, guard, tc::WAIT_TMEM_FULL, local)) break;
+            tc::tc_fence_after_sync();
+            const int row = tm * BM + rank * HALF + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+            for (int cb = 0; cb < BN; cb += 32) {
+                uint32_t r[32];
+                tc::tmem_ld_32x32(taddr + cb, r);
+                tc::tmem_ld_wait();
+                if (EPI != EPI_NONE) {
+#pragma unroll
+                    for (int x = 0; x < 32; ++x) r[x] = __float_as_uint(gemm_epilogue<EPI>(__uint_as_float(r[x]), scale));
+                }
+                const int col = tn * BN + cb;
+                if (row < shape.m) {
+                    out_t* dst = c + static_cast<size_t>(row) * shape.n + col;
+                    if (vec_ok && col + 32 <= shape.n) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint4 v;
+                            v.x = pack2<BF16>(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1]));
+                            v.y = pack2<BF16>(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]));
+                            v.z = pack2<BF16>(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
+                            v.w = pack2<BF16>(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
+                            *reinterpret_cast<uint4*>(dst + 8 * q) = v;
+                        }
+                    } else {
+                        for (int j = 0; j < 32; ++j)
+                            if (col + j < shape.n) {
+                                uint32_t p = pack2<BF16>(__uint_as_float(r[j]), 0.0f);
+                                dst[j] = *reinterpret_cast<out_t*>(&p);
+                            }
+                    }
+                }
+            }
+            tc::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive_cluster(tc::smem_of_cta(&tmem_empty[buf], 0));
+        }
+    }
+
+    // teardown: both CTAs meet (neither may leave while the other can still read its shared memory or arrive
+    // on its barriers), then the allocating warp of each frees the tensor memory
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::cluster_sync();
+    if (warp == 1) {
+        tc::tc_fence_after_sync();
+        tc::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
 }  // namespace emb

@@ -31,6 +31,9 @@ from .ir import dtype_name, kind
 TARGET_SMS = 148
 GEMM_STAGES = 4
 GEMM_GROUP_M = 16
+GEMM_PAIR_STAGES = 6      # CTA pairs: a stage is 32 KB per CTA
+GEMM_PAIR_GROUP_M = 8     # in 256-row tiles: the same L2 footprint as 16 row-blocks of 128
+GEMM_PAIR_MIN_TILES = 74  # CTA pairs (256 x 256 tiles) only when they give every TPC of the GPU a tile; 0 switches them off
 ATTN_POLY_PERIOD = 4  # every n-th pair of softmax weights gets its 2^x from an FMA polynomial instead of the SFU (0: none)
 
 
@@ -67,6 +70,25 @@ def tmap(name: str, buffer: str, dtype: str, dims, strides_bytes, box, swizzle: 
 
 
 # ---------------------------------------------------------------- matmul
+
+
+def gemm_geometry(M: int, N: int, elem_bytes: int = 2) -> dict:
+    """How the matmul template walks an M x N result: lone CTAs on 128 x 256 tiles, or - when there are enough
+    256 x 256 tiles to give every pair of SMs one - clusters of two CTAs that run each tile as one
+    tcgen05.mma.cta_group::2 (half the operand bytes per CTA for the same tensor work, a deeper ring)."""
+    pair_tiles = math.ceil(M / 256) * math.ceil(N / 256)
+    if GEMM_PAIR_MIN_TILES and pair_tiles >= GEMM_PAIR_MIN_TILES:
+        stage = (128 + 128) * 128
+        return dict(kernel="gemm_tn_pair_kernel", stages=GEMM_PAIR_STAGES, group=GEMM_PAIR_GROUP_M, b_rows=128, tiles=pair_tiles,
+                    tile="256 x 256", grid=2 * min(TARGET_SMS // 2, pair_tiles), cluster=2, stage=stage,
+                    smem=GEMM_PAIR_STAGES * stage + 1024 + 256,
+                    how="clusters of two CTAs (one tcgen05.mma.cta_group::2 of 256 x 256 x 16 per step; each CTA loads and "
+                        "drains its 128 rows)")
+    tiles = math.ceil(M / 128) * math.ceil(N / 256)
+    stage = (128 + 256) * 128
+    return dict(kernel="gemm_tn_kernel", stages=GEMM_STAGES, group=GEMM_GROUP_M, b_rows=256, tiles=tiles, tile="128 x 256",
+                grid=min(TARGET_SMS, tiles), cluster=1, stage=stage, smem=GEMM_STAGES * stage + 1024 + 256,
+                how="persistent CTAs")
 
 
 def match_matmul(src, strict: bool) -> Plan:
@@ -108,24 +130,21 @@ def match_matmul(src, strict: bool) -> Plan:
     need(M * N >= 128 * 256 // 4, "too small for a 128 x 256 tensor-core tile")
 
     bf16 = A.dtype == "bf16"
-    tiles = math.ceil(M / 128) * math.ceil(N / 256)
-    grid = min(TARGET_SMS, tiles)
-    stage = (128 + 256) * 64 * 2
-    smem = GEMM_STAGES * stage + 1024 + 256
-    call = [f"    emb::gemm_tn_kernel<{GEMM_STAGES}, {GEMM_GROUP_M}, {str(bf16).lower()}>(&tmap_a, &tmap_b, p_{write.output}, "
+    g = gemm_geometry(M, N)
+    call = [f"    emb::{g['kernel']}<{g['stages']}, {g['group']}, {str(bf16).lower()}>(&tmap_a, &tmap_b, p_{write.output}, "
             f"emb::GemmShape{{{M}, {N}, {K}}}, status);"]
     extra_sig = ["const __grid_constant__ CUtensorMap tmap_a", "const __grid_constant__ CUtensorMap tmap_b",
                  "unsigned* __restrict__ status"]
     source = wrapper(src, '#include "emb_gemm.cuh"', call, extra_sig, 192)
     extra = [tmap("a", a.input, A.dtype, (K, M), (K * 2,), (64, 128)),
-             tmap("b", b.input, B.dtype, (K, N), (K * 2,), (64, 256)),
+             tmap("b", b.input, B.dtype, (K, N), (K * 2,), (64, g["b_rows"])),
              dict(kind="status", name="status")]
-    remarks = [f"tensor-core matmul template: {M} x {N} x {K} {A.dtype}, f32 accumulation in tensor memory; {tiles} tiles of "
-               f"128 x 256 walked by {grid} persistent CTAs of 192 threads (TMA producer, tcgen05.mma issuer, 4 epilogue warps)",
-               f"TMA tensor-map loads (128-byte swizzle, no multicast) into {GEMM_STAGES} stages of {stage} B on mbarriers; "
+    remarks = [f"tensor-core matmul template: {M} x {N} x {K} {A.dtype}, f32 accumulation in tensor memory; {g['tiles']} tiles of "
+               f"{g['tile']} walked by {g['grid']} CTAs of 192 threads (TMA producer, tcgen05.mma issuer, 4 epilogue warps): {g['how']}",
+               f"TMA tensor-map loads (128-byte swizzle, no multicast) into {g['stages']} stages of {g['stage']} B on mbarriers; "
                "two 256-column TMEM accumulators so that a tile's epilogue overlaps the next tile's MMAs",
-               f"tile order: {GEMM_GROUP_M} row-blocks share each B panel in L2"]
-    return Plan("tensorcore", source, remarks, grid=grid, block=192, smem_bytes=smem, extra_params=extra)
+               f"tile order: {g['group']} row-blocks share each B panel in L2"]
+    return Plan("tensorcore", source, remarks, grid=g["grid"], block=192, cluster=g["cluster"], smem_bytes=g["smem"], extra_params=extra)
 
 
 def match_matmul_e4m3(src, strict: bool) -> Plan:

@@ -35,6 +35,24 @@ def test_matmul_small_against_the_oracle(tmp_path, m, n, k, dtype):
     check(got, want, dtype)
 
 
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (512, 768, 320), (384, 512, 1024), (200, 264, 72), (100, 256, 128), (1280, 1024, 256)])
+def test_matmul_on_cta_pairs_against_the_oracle(tmp_path, monkeypatch, m, n, k, dtype):
+    """The cta_group::2 walk (256 x 256 tiles on clusters of two CTAs), which the matcher only picks for results
+    with at least one tile per pair of SMs, forced onto small and ragged shapes: rows past M in the second CTA
+    of a pair (200), a second CTA with no rows at all (100), several tiles per pair (1280 x 1024)."""
+    from emmy_ptx import tcfamilies
+    monkeypatch.setattr(tcfamilies, "GEMM_PAIR_MIN_TILES", 1)
+    block = 64 if (m * n) % 256 else 256
+    p = problems.matmul_f16(m=m, n=n, k=k, block=block, dtype=dtype, ident="t")
+    prob = runner.Problem(problems.write(p, tmp_path), "optimized")
+    info = prob.kernels[0].launch_info
+    assert info["family"] == "tensorcore" and info["cluster"] == 2 and "cta_group::2" in prob.kernels[0].ptx
+    want = oracle_problem(p, prob.host)["matmul"]
+    for _ in range(2):  # a second launch finds every barrier and the tensor memory as a first one does
+        check(prob.run()["matmul"], want, dtype)
+
+
 def test_matmul_strict_and_plain_keep_the_ir_order(tmp_path):
     """--strict refuses the template (another summation order) and is bit-exact through the statement lowering."""
     from helpers import same_bits
