@@ -43,6 +43,7 @@ template <> __device__ __forceinline__ uint32_t pack2<true>(float lo, float hi) 
 
 struct GemmShape {
     int m, n, k;
+    int splits = 1;  // K is cut into this many slabs (each a multiple of 64 when there are several); C is [splits, m, n]
 };
 
 // What the epilogue does to an accumulator before it is rounded to the output type.
@@ -61,7 +62,9 @@ template <int EPI> __device__ __forceinline__ float gemm_epilogue(float acc, flo
 // FP8: the operands are e4m3 byte codes (tcgen05 kind::f8f6f4, 128 elements per 128-byte row, K = 32 per MMA);
 // otherwise 16-bit (kind::f16, 64 elements per row, K = 16 per MMA). BF16 names the OUTPUT type (and, for the
 // 16-bit kind, the operand type).
-template <int STAGES, int GROUP_M, bool BF16, int EPI = EPI_NONE, bool FP8 = false>
+// B_NMAJOR: B is stored [K, N] (N contiguous) instead of [N, K]: its stage is four boxes of 64 columns x 64 k, read
+// through an MN-major descriptor. OUT_F32: C is f32 (the partial slabs of a split-K schedule) instead of 16-bit.
+template <int STAGES, int GROUP_M, bool BF16, int EPI = EPI_NONE, bool FP8 = false, bool B_NMAJOR = false, bool OUT_F32 = false>
 __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ map_a, const CUtensorMap* __restrict__ map_b,
                                                void* __restrict__ c_out, GemmShape shape, unsigned* status,
                                                const float* __restrict__ scale_ptr = nullptr) {
@@ -85,8 +88,10 @@ __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ m
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (shape.m + BM - 1) / BM, tiles_n = (shape.n + BN - 1) / BN;
-    const int num_tiles = tiles_m * tiles_n;
-    const int k_blocks = (shape.k + BK - 1) / BK;
+    const int tiles_mn = tiles_m * tiles_n;
+    const int num_tiles = tiles_mn * shape.splits;
+    const int k_slab = shape.k / shape.splits;
+    const int k_blocks = (k_slab + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -110,7 +115,9 @@ __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ m
 
     // tile order: GROUP_M row-blocks at a time, all column-blocks under them, so that the CTAs running
     // together share A and B panels in L2
-    auto tile_coords = [&](int t, int& tm, int& tn) {
+    auto tile_coords = [&](int t, int& tm, int& tn, int& slab) {
+        slab = t / tiles_mn;
+        t -= slab * tiles_mn;
         const int per_group = GROUP_M * tiles_n;
         const int g = t / per_group, r = t % per_group;
         const int rows = min(GROUP_M, tiles_m - g * GROUP_M);
@@ -123,8 +130,8 @@ __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ m
             uint32_t it = 0;
             bool alive = true;
             for (int t = blockIdx.x; alive && t < num_tiles; t += gridDim.x) {
-                int tm, tn;
-                tile_coords(t, tm, tn);
+                int tm, tn, slab;
+                tile_coords(t, tm, tn, slab);
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                     if (!tc::mbar_wait(&empty[s], ph ^ 1, guard, tc::WAIT_SMEM_EMPTY, it)) {
@@ -133,14 +140,21 @@ __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ m
                     }
                     tc::mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
                     uint8_t* stage = smem + s * STAGE_BYTES;
-                    tc::tma_load_2d(stage, map_a, &full[s], kb * BK, tm * BM);
-                    tc::tma_load_2d(stage + A_BYTES, map_b, &full[s], kb * BK, tn * BN);
+                    const int k0 = slab * k_slab + kb * BK;
+                    tc::tma_load_2d(stage, map_a, &full[s], k0, tm * BM);
+                    if (B_NMAJOR) {
+#pragma unroll
+                        for (int b = 0; b < BN / 64; ++b)
+                            tc::tma_load_2d(stage + A_BYTES + b * (B_BYTES / (BN / 64)), map_b, &full[s], tn * BN + b * 64, k0);
+                    } else {
+                        tc::tma_load_2d(stage + A_BYTES, map_b, &full[s], k0, tn * BN);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         if (tc::elect_one()) {
-            constexpr uint32_t idesc = FP8 ? tc::idesc_e4m3(BM, BN) : tc::idesc_f16(BM, BN, BF16);
+            constexpr uint32_t idesc = (FP8 ? tc::idesc_e4m3(BM, BN) : tc::idesc_f16(BM, BN, BF16)) | (B_NMAJOR ? 1u << 16 : 0u);
             uint32_t it = 0, local = 0;
             bool alive = true;
             for (int t = blockIdx.x; alive && t < num_tiles; t += gridDim.x, ++local) {
@@ -161,6 +175,9 @@ __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ m
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         if (FP8)
                             tc::mma_e4m3_ss(d_tmem, a_desc + (k * 32 >> 4), b_desc + (k * 32 >> 4), idesc, (kb | k) != 0);
+                        else if (B_NMAJOR)  // 16 k = 16 rows of 128 bytes further on; 64-column groups 8 KB apart
+                            tc::mma_f16_ss(d_tmem, a_desc + (k * 32 >> 4),
+                                           tc::smem_desc_mn128(stage + A_BYTES + k * UMMA_K * 128, B_BYTES / (BN / 64)), idesc, (kb | k) != 0);
                         else
                             tc::mma_f16_ss(d_tmem, a_desc + (k * 32 >> 4), b_desc + (k * 32 >> 4), idesc, (kb | k) != 0);
                     }
@@ -177,8 +194,8 @@ __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ m
         const bool vec_ok = (shape.n % 8) == 0;
         const float scale = (EPI != EPI_NONE && scale_ptr) ? __ldg(scale_ptr) : 1.0f;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
-            int tm, tn;
-            tile_coords(t, tm, tn);
+            int tm, tn, slab;
+            tile_coords(t, tm, tn, slab);
             const uint32_t buf = local & 1, use = local >> 1;
             if (!tc::mbar_wait(&tmem_full[buf], use & 1, guard, tc::WAIT_TMEM_FULL, local)) break;
             tc::tc_fence_after_sync();
@@ -194,8 +211,20 @@ __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ m
                     for (int x = 0; x < 32; ++x) r[x] = __float_as_uint(gemm_epilogue<EPI>(__uint_as_float(r[x]), scale));
                 }
                 const int col = tn * BN + cb;
-                if (row < shape.m) {
-                    out_t* dst = c + static_cast<size_t>(row) * shape.n + col;
+                if (OUT_F32) {
+                    if (row < shape.m) {
+                        float* dst = static_cast<float*>(c_out) + (static_cast<size_t>(slab) * shape.m + row) * shape.n + col;
+                        if ((shape.n % 4) == 0 && col + 32 <= shape.n) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                *reinterpret_cast<uint4*>(dst + 4 * q) = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                        } else {
+                            for (int j = 0; j < 32; ++j)
+                                if (col + j < shape.n) dst[j] = __uint_as_float(r[j]);
+                        }
+                    }
+                } else if (row < shape.m) {
+                    out_t* dst = c + (static_cast<size_t>(slab) * shape.m + row) * shape.n + col;
                     if (vec_ok && col + 32 <= shape.n) {
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {

@@ -223,6 +223,19 @@ __device__ __forceinline__ uint64_t smem_desc_k128(const void* tile) {
     return d;
 }
 
+// The same for an MN-major operand tile (the operand stored with its M or N index contiguous, e.g. B kept as
+// [K, N]): boxes of 64 columns x (k rows of 128 bytes); `tile` is the first of the 16 k-rows of this MMA step,
+// 64-column groups are `group_bytes` apart (leading offset), 8-row groups 1024 bytes (stride offset).
+__device__ __forceinline__ uint64_t smem_desc_mn128(const void* tile, uint32_t group_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_u32(tile) & 0x3ffff) >> 4);
+    d |= static_cast<uint64_t>(group_bytes >> 4) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
 // Instruction descriptor of kind::f16 (A, B f16 or bf16; D f32) with both operands K-major.
 __host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool a_bf16, bool b_bf16) {
     return (1u << 4) | ((a_bf16 ? 1u : 0u) << 7) | ((b_bf16 ? 1u : 0u) << 10) | (static_cast<uint32_t>(n >> 3) << 17) |

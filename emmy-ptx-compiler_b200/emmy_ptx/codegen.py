@@ -32,7 +32,7 @@ from __future__ import annotations
 
 import math
 
-from . import clusterize, ir
+from . import clusterize, fragcode, ir
 from .ir import dtype_name, kind
 
 CTYPE = {"f32": "float", "f64": "double", "f16": "__half", "bf16": "__nv_bfloat16", "i8": "signed char",
@@ -49,7 +49,7 @@ INT_OPS = {"add", "subtract", "multiply", "floor_divide", "remainder", "mod", "l
            "bitwise_or", "bitwise_xor", "bitwise_count"}
 WIDTH = {"u8": 8, "i16": 16, "u16": 16, "i32": 32, "u32": 32, "i64": 64, "u64": 64}
 COMPARE = {"equal": "==", "not_equal": "!=", "greater": ">", "less": "<", "greater_equal": ">=", "less_equal": "<="}
-CROSS_THREAD = ("WarpShuffle", "TreeHalve", "Sync")
+CROSS_THREAD = ("WarpShuffle", "TreeHalve", "Sync") + fragcode.WARP_WIDE
 
 
 class CodegenError(Exception):
@@ -97,8 +97,11 @@ def divisible(e, k: int, facts: dict) -> bool:
     return False
 
 
-class Emitter:
+class Emitter(fragcode.FragmentStatements):
     def __init__(self, src, plain: bool = False, strict: bool = False):
+        self.frags: dict = {}  # fragment name -> (role, element dtype, members, registers)
+        self.frag_decls: list = []
+        self.smem_align: dict = {}
         self.src, self.plain, self.strict = src, plain, strict
         self.lines: list = []
         self.depth = 1
@@ -460,7 +463,30 @@ class Emitter:
         self.emit(f"{v} = {last};")
 
     def x_StridedLoop(self, s, guard) -> None:
-        raise CodegenError("a cross-thread statement inside a strided loop")
+        """A strided loop around cross-thread statements: every thread of the block must make the same trips, which
+        literal bounds guarantee (the K loops of the fragment form); threads outside ``guard`` walk along idle."""
+        if not (kind(s.start) == "Literal" and kind(s.step) == "Literal" and (s.end is None or kind(s.end) == "Literal")):
+            raise CodegenError("a cross-thread statement inside a strided loop whose bounds are not literals")
+        if guard is not None:
+            self.emit(f"if ({guard}) {{")
+            self.depth += 1
+        self.seed(s)
+        if guard is not None:
+            self.depth -= 1
+            self.emit("}")
+        v = self.var(s.axis.name, "i64")
+        end = int(s.end.value) if s.end is not None else int(s.axis.extent.as_static())
+        it = f"it_{s.axis.name}"
+        if s.unroll:
+            self.emit("#pragma unroll")
+        self.emit(f"for (long long {it} = {int(s.start.value)}LL; {it} < {end}LL; {it} += {int(s.step.value)}LL) {{")
+        self.depth += 1
+        self.loop_depth += 1
+        self.emit(f"{v} = {it};" if guard is None else f"if ({guard}) {v} = {it};")
+        self.block(s.body, guard)
+        self.loop_depth -= 1
+        self.depth -= 1
+        self.emit("}")
 
     def s_Cond(self, s) -> None:
         self.emit(f"if {self.truth(s.cond)} {{")
@@ -529,6 +555,7 @@ class Emitter:
         if dt not in CTYPE:
             raise CodegenError(f"shared array of {ctype}")
         self.shared[s.name] = (dt, tuple(int(n) for n in s.extents))
+        self.smem_align[s.name] = max(16, int(getattr(s, "align", 0) or 0))
 
     def memory(self, name: str) -> tuple:
         """(C array, element dtype, shape, is_shared, read_only)"""
@@ -758,11 +785,12 @@ def generate(src, plain: bool = False, strict: bool = False, disable=()) -> tupl
     em.disable = frozenset(disable)
     em.block(src.body, None)
     decls = [f"    {CTYPE[dt]} v_{name} = emb::zero<{CTYPE[dt]}>();" for name, dt in em.vars.items() if name not in ("lane", "warp")]
-    smem = [f"    __shared__ {CTYPE[dt]} s_{name}[{math.prod(shape)}];" for name, (dt, shape) in em.shared.items()]
+    smem = [f"    __shared__ __align__({em.smem_align.get(name, 16)}) {CTYPE[dt]} s_{name}[{math.prod(shape)}];"
+            for name, (dt, shape) in em.shared.items()]
     attrs = f"__cluster_dims__({em.cluster}, 1, 1) " if em.cluster > 1 else ""
-    head = [f"#define EMB_STRICT {int(strict)}", PRELUDE,
+    head = [f"#define EMB_STRICT {int(strict)}", PRELUDE + ('#include "emb_frag.cuh"\n' if em.frags else ""),
             f'extern "C" __global__ void {attrs}__launch_bounds__({src.launch.block}) {src.name}({signature(src)}) {{',
             "    const unsigned emb_warp = __activemask();",
             "    int v_lane = threadIdx.x & 31, v_warp = threadIdx.x >> 5;",
             "    (void)emb_warp; (void)v_lane; (void)v_warp;"] + pdl_prologue(src, not plain)
-    return "\n".join(head + smem + decls + em.lines + ["}"]) + "\n", em.remarks, em.cluster
+    return "\n".join(head + smem + decls + em.frag_decls + em.lines + ["}"]) + "\n", em.remarks, em.cluster

@@ -281,13 +281,88 @@ KNOWN = {c.__name__: c for c in (
     StridedLoop, Cond, Load, Write, Assign, Accum, Let, Init, SelectBranch, Select, Smem, Sync, WarpShuffle,
     TreeHalve)}
 
-# Statement kinds of emmy's tensor-core (fragment) form and its asynchronous copies: read and
-# printed like the rest, but no lowering here takes them (they are not in the interpreter's subset).
+# ---------------------------------------------------------------- the tensor-core (fragment) form
+#
+# emmy's warp-level statements for mma.sync m16n8k16 and the asynchronous copies that feed them, with the fields
+# and defaults the reference's lowering reads (emmy_ptx/tensorcore.py:147-420, emmy_ptx/lower.py:1057-1102).
+
+
+class CpAsyncCopy(Node):
+    _fields = (("smem", _MISSING), ("smem_index", _MISSING), ("src", _MISSING), ("src_index", _MISSING), ("nbytes", 16),
+               ("swizzle", "NONE"), ("lane_index", None), ("lane_rows", None))
+
+
+class CpAsyncCommit(Node):
+    _fields = ()
+
+
+class CpAsyncWait(Node):
+    _fields = (("group", 0),)
+
+
+class RegFragment(Node):
+    _fields = (("name", _MISSING), ("role", _MISSING), ("shape", (16, 8, 16)), ("dtype", "f16"), ("count", 1), ("nregs", None))
+
+    def _coerce(self):
+        self.dtype = datatype(self.dtype)
+
+
+class LdmatrixLoad(Node):
+    _fields = (("frag", _MISSING), ("src_buffer", _MISSING), ("src_index", _MISSING), ("role", _MISSING), ("ldm", 0),
+               ("swizzle", "NONE"), ("staged", True), ("gmem_guard", None), ("k_zero", None), ("b_trans", False),
+               ("pair_frag", None), ("byte_slab", False), ("scale_buffer", None), ("scale_index", ()), ("scale_ldm", 0),
+               ("fragment_layout", "m16n8k16"), ("fragment_index", 0))
+
+
+class MmaSyncPtx(Node):
+    _fields = (("c_frag", _MISSING), ("a_frag", _MISSING), ("b_frag", _MISSING), ("shape", (16, 8, 16)), ("ab_dtype", "f16"),
+               ("c_dtype", "f32"), ("b_row_major", False), ("sfa_frag", None), ("sfb_frag", None))
+
+    @property
+    def block_scaled(self) -> bool:
+        return self.sfa_frag is not None or self.sfb_frag is not None
+
+
+class RegStore(Node):
+    _fields = (("dst_buffer", _MISSING), ("dst_index", _MISSING), ("frag", _MISSING), ("shape", (16, 8, 16)), ("ldm", 0),
+               ("epilogue", None), ("extra_frags", ()), ("m_guard", None), ("n_guard", None), ("atomic", False),
+               ("fragment_layout", "m16n8k16"), ("volta_interleaved", False), ("fragment_index", (0, 0)),
+               ("swizzle", "NONE"), ("row_dim", None), ("col_dim", None))
+
+
+class FragmentApply(Node):
+    _fields = (("out", _MISSING), ("op", _MISSING), ("args", _MISSING), ("kinds", _MISSING), ("in_place", False),
+               ("row_base", None), ("col_base", None), ("post", ()), ("layout", None))
+
+
+class FragmentRowReduce(Node):
+    _fields = (("frags", _MISSING), ("op", _MISSING), ("top", _MISSING), ("bot", _MISSING), ("layout", None))
+
+
+class FragmentRepack(Node):
+    _fields = (("frag", _MISSING), ("srcs", _MISSING), ("ab_dtype", "f16"), ("fragment_layout", "m16n8k16"))
+
+
+class FragmentPromote(Node):
+    _fields = (("dst", _MISSING), ("src", _MISSING))
+
+
 FRAGMENT_FORM = ("CpAsyncCopy", "CpAsyncCommit", "CpAsyncWait", "RegFragment", "LdmatrixLoad", "MmaSyncPtx", "RegStore",
-                 "ZeroPrologue", "FragmentApply", "FragmentRowReduce", "FragmentRepack", "FragmentPromote",
-                 "FuncCallExpr", "Builtin", "FlatIndex")
-for _name in FRAGMENT_FORM:
+                 "FragmentApply", "FragmentRowReduce", "FragmentRepack", "FragmentPromote")
+for _cls in (CpAsyncCopy, CpAsyncCommit, CpAsyncWait, RegFragment, LdmatrixLoad, MmaSyncPtx, RegStore, FragmentApply,
+             FragmentRowReduce, FragmentRepack, FragmentPromote):
+    KNOWN[_cls.__name__] = _cls
+# read and printed like the rest, taken by no lowering here
+for _name in ("ZeroPrologue", "FuncCallExpr", "Builtin", "FlatIndex", "FragmentLayout", "Epilogue"):
     KNOWN[_name] = type(_name, (Node,), {})
+
+
+def fragment_ref(ref: str) -> tuple:
+    """``name`` or ``name[i]`` as (name, index): the index an int, a variable name, or None."""
+    if ref.endswith("]") and "[" in ref:
+        name, _, index = ref[:-1].partition("[")
+        return name, (int(index) if index.isdigit() else index)
+    return ref, None
 
 
 # ---------------------------------------------------------------- reader
@@ -331,7 +406,9 @@ def _build(n):
         if name == "float" and len(args) == 1:  # float('inf'), float('-inf'), float('nan')
             return float(args[0])
         if name not in KNOWN:
-            raise IRSyntaxError(f"unknown node {name!r}")
+            if args:  # a record this reader has no declaration for is taken by its keywords alone
+                raise IRSyntaxError(f"unknown node {name!r}")
+            KNOWN[name] = type(name, (Node,), {})
         return KNOWN[name](*args, **kw)
     raise IRSyntaxError(f"unexpected syntax {ast.dump(n)[:80]}")
 

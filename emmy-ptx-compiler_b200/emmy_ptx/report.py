@@ -26,6 +26,9 @@ CENSUS = [
     ("atomic", "atomics", r"(red|atom)\."),
     ("TMA copy", "TMA copies", r"cp\.async\.bulk"),
     ("mbarrier op", "mbarrier ops", r"mbarrier\."),
+    ("cp.async copy", "cp.async copies", r"cp\.async\.(ca|cg)"),
+    ("ldmatrix", "ldmatrix", r"ldmatrix\."),
+    ("warp mma", "warp mma", r"mma\.sync"),
     ("tcgen05 mma", "tcgen05 mma", r"tcgen05\.mma"),
     ("tensor-memory access", "tensor-memory accesses", r"tcgen05\.(ld|st|cp)"),
     ("shuffle", "shuffles", r"shfl\."),
