@@ -50,6 +50,10 @@ WORKLOADS = {
     "mlp": dict(folder="k_mlp_gelu_tanh_16384x4096x16384", bound="tensor", flops=2 * 16384 * 4096 * 16384, dominant=2,
                 chain_flops=2 * 2 * 16384 * 4096 * 16384, dtype="bf16",
                 describe="GELU MLP 16384x4096x16384, bf16 x, e4m3 weights decoded to bf16, bf16 tcgen05 MMA (BASELINE configs[4])"),
+    # the same product handed over as a warp-level mma.sync schedule (fragment form) plus its fold kernel: optimized mode proves
+    # it a matmul and runs the tcgen05 template, --mode plain runs the schedule as written (what the reference's lowering emits)
+    "fragments": dict(folder="m_f16_8192_fragments", bound="tensor", flops=2 * 8192 ** 3, dominant=0, dtype="f16", oracle="fragment",
+                      describe="f16 GEMM 8192^3 given in fragment form (mma.sync schedule, B stored N x K) + fold kernel"),
 }
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (None until captured)
@@ -120,9 +124,9 @@ _JOB = None  # (body, buffers, grid, block) of the oracle run the forked workers
 
 
 def _oracle_share(blocks):
-    from oracle import ir_oracle
+    from oracle import fragment_oracle  # runs plain bodies as ir_oracle does, and the tensor-core statements
     body, bufs, grid, block = _JOB
-    ir_oracle.run(body, bufs, grid, block, blocks=blocks)
+    fragment_oracle.run(body, bufs, grid, block, blocks=blocks)
     return len(blocks)
 
 
@@ -136,6 +140,8 @@ def oracle_sample(workload: str, budget_s: float, workers: int) -> dict:
     import numpy as np
     from emmy_ptx import problems, runner
     from oracle import ir_oracle
+    if WORKLOADS[workload].get("oracle") == "fragment":  # the interpreter's extension to the tensor-core statements
+        from oracle import fragment_oracle as ir_oracle
     make = problems.WORKLOADS[workload]
     p = make()
     meta_args = json.loads((PKG / "problems" / WORKLOADS[workload]["folder"] / "meta.json").read_text())["kernels"]
@@ -197,7 +203,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="softmax", choices=sorted(WORKLOADS))
-    ap.add_argument("--mode", default="optimized", choices=("optimized", "strict"))
+    ap.add_argument("--mode", default="optimized", choices=("optimized", "strict", "plain"))
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--buffer-sets", type=int, default=0, help="copies of every buffer the passes rotate through (0: enough "

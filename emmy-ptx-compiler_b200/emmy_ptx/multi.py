@@ -22,7 +22,8 @@ def shard(units: int, rank: int, world: int) -> range:
 
 
 SHARDED_AXIS = {"sum": "elements", "softmax": "rows", "matmul": "rows of A and C (B replicated)",
-                "attention": "(batch, head) pairs", "mlp": "token rows (weights replicated)"}
+                "attention": "(batch, head) pairs", "mlp": "token rows (weights replicated)",
+                "fragments": "rows of A and C (B replicated)"}
 
 
 def combine_sum(partial, strict: bool = False, group=None):

@@ -389,9 +389,17 @@ def write(problem: dict, root) -> Path:
     return folder
 
 
-WORKLOADS = {"sum": array_sum, "softmax": row_softmax, "matmul": matmul_f16, "attention": attention, "mlp": gelu_mlp}
+def matmul_fragments(m: int = 8192, n: int = 8192, k: int = 8192, ident: str = "m_f16_8192_fragments"):
+    """The matmul workload as emmy hands tensor-core kernels over: a warp-level mma.sync schedule (B stored N x K,
+    one K-slab) and the fold kernel behind it, in the form of examples/m_f16_128 of the reference."""
+    from . import fragproblems
+    return fragproblems.fragment_matmul(m=m, n=n, k=k, splits=1, dtype="f16", b_layout="nk", ident=ident)
+
+
+WORKLOADS = {"sum": array_sum, "softmax": row_softmax, "matmul": matmul_f16, "attention": attention, "mlp": gelu_mlp,
+             "fragments": matmul_fragments}
 
 
 def write_all(root) -> list:
-    """The five full-size workloads."""
+    """The five full-size workloads, and the matmul once more in fragment form."""
     return [write(make(), root) for make in WORKLOADS.values()]
