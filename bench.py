@@ -15,8 +15,9 @@ reference's numpy interpreter) timed on a bounded sample of the same workload.
 
 Multi-GPU: launched by torchrun with one rank per GPU. The workloads shard without any data-path
 exchange (rows, batch*heads, element ranges), every rank runs the full single-GPU workload on its
-own shard of an N-times larger job (weak scaling); the array sum adds its one exchange, an NCCL
-all-reduce of the per-GPU scalar.
+own shard of an N-times larger job (weak scaling); the array sum adds its one exchange: the per-GPU
+scalars are combined inside the sum's last kernel by peer stores into symmetric memory and a bounded
+wait (``--exchange nccl``, or a box without such memory: an NCCL all-reduce after the kernel).
 """
 
 from __future__ import annotations
@@ -204,6 +205,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="softmax", choices=sorted(WORKLOADS))
     ap.add_argument("--mode", default="optimized", choices=("optimized", "strict", "plain"))
+    ap.add_argument("--exchange", default="fused", choices=("fused", "nccl"),
+                    help="several GPUs, the array sum: combine the per-GPU scalars inside the last kernel, or by NCCL after it")
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--buffer-sets", type=int, default=0, help="copies of every buffer the passes rotate through (0: enough "
@@ -237,18 +240,30 @@ def main() -> None:
 
     def measure(workload: str, steps: int, with_e2e: bool):
         w = WORKLOADS[workload]
-        prob = runner.Problem(PKG / "problems" / w["folder"], args.mode, device=local)
+        exchange, how = None, None
+        if workload == "sum" and world > 1:
+            # the one real exchange of the path: the per-GPU scalars are combined inside the sum's last kernel (peer stores
+            # into symmetric memory, bounded wait); an NCCL all-reduce after the kernel only if that memory cannot be had
+            how = "in-kernel (peer stores + bounded wait, emb_peer.cuh)"
+            if args.exchange == "fused":
+                try:
+                    exchange = multi.PeerExchange.create()
+                except Exception as e:  # every rank fails alike (no fabric / IPC handles on this box)
+                    how = f"NCCL all-reduce after the kernel (symmetric memory unavailable: {type(e).__name__}: {e})"[:240]
+            else:
+                how = "NCCL all-reduce after the kernel (--exchange nccl)"
+        prob = runner.Problem(PKG / "problems" / w["folder"], args.mode, device=local, exchange=exchange)
         stream = prob.stream
         if args.buffer_sets == 1:
             nsets = 1
         else:  # the buffer sets together exceed the 126 MB L2: every pass is cold
             nsets = prob.rotate(min_bytes=512 << 20, max_sets=args.buffer_sets or 8)
-        set_bytes = sum(t.numel() * t.element_size() for t in prob.tensors.values())
-        exchange = workload == "sum" and world > 1
+        set_bytes = sum(t.numel() * t.element_size() for n, t in prob.tensors.items() if n != runner.EXCHANGE)
+        nccl = workload == "sum" and world > 1 and exchange is None
         barrier()
-        if not exchange:
+        if not nccl:
             total_us = prob.time_rotating_us(warmup=warmup, iters=1, batch=steps)[0] * steps
-        else:  # the one real exchange of the path: an all-reduce of the per-GPU scalar, inside every step
+        else:
             finals = [prob.tensors["sum_1"]] + [c["sum_1"] for c in getattr(prob, "copies", [])]
             for i in range(warmup):
                 driver.launch(prob.sets[i % nsets], stream)
@@ -269,7 +284,7 @@ def main() -> None:
         per_launch = prob.time_rotating_us(warmup=3, iters=max(10, min(steps, 50)), batch=1)  # one event pair per pass
         # the dominant kernel alone over the same kind of timed region, for the roofline (the pass itself when it is one launch)
         entries = [e for k in prob.kernels for e in [p_["entry"] for p_ in k.launch_info.get("pre", ())] + [k.meta["entry"]]]
-        if len(prob.launches) == 1 and not exchange:
+        if len(prob.launches) == 1 and not nccl:
             dom_us = mean_us
         else:
             dom_us = prob.time_rotating_us(warmup=warmup, iters=1, batch=steps, only=w["dominant"])[0]
@@ -285,6 +300,8 @@ def main() -> None:
                     traffic=NCU_TRAFFIC.get(workload), kernel=entries[w["dominant"]], kernel_us=dom_us,
                     peak_source=f"of {pk_kind}", family=prob.kernels[-1 if w["dominant"] else 0].launch_info.get("family"))
         timing = dict(buffer_sets=nsets, bytes_per_set=set_bytes, us_per_pass_with_an_event_pair_each=statistics.median(per_launch))
+        if how:
+            timing["exchange"] = how
         e2e = None
         if with_e2e:
             ins = {n: prob.tensors[n] for n in prob.host}

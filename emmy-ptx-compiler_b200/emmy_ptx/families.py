@@ -189,11 +189,11 @@ def tile_decode(em: Emitter, tile, block: int) -> None:
         stride *= n
 
 
-def finish(em: Emitter, src, includes: str, strict: bool, shared: list, min_blocks=None) -> str:
+def finish(em: Emitter, src, includes: str, strict: bool, shared: list, min_blocks=None, extra_sig=()) -> str:
     decls = [f"    {CTYPE[dt]} v_{n} = emb::zero<{CTYPE[dt]}>();" for n, dt in em.vars.items() if n not in ("lane", "warp")]
     head = [f"#define EMB_STRICT {int(strict)}", includes, codegen.PRELUDE.split("\n", 1)[1],
             f'extern "C" __global__ void __launch_bounds__({src.launch.block}{f", {min_blocks}" if min_blocks else ""}) '
-            f'{src.name}({codegen.signature(src)}) {{',
+            f'{src.name}({", ".join([codegen.signature(src), *extra_sig])}) {{',
             "    int v_lane = threadIdx.x & 31, v_warp = threadIdx.x >> 5;", "    (void)v_lane; (void)v_warp;",
             "    const unsigned emb_warp = 0xffffffffu; (void)emb_warp;"] + codegen.pdl_prologue(src, True)
     return "\n".join(head + shared + decls + em.lines + ["}"]) + "\n"
@@ -272,10 +272,14 @@ def match_reduce(src, strict: bool) -> Plan:
             f"{pointer}, {start}, {step}, {end});")
     em.emit(f"acc_ = emb::block_combine<{OP_TYPE[comb.shuffle_op]}, {comb.shuffle_len}, {tree_op}, {comb.tree_len}>"
             f"(acc_, emb_slab);")
+    exchange = final_sum(src, op, comb, tail, state)
+    if exchange:  # the last kernel of a sum: its scalar may be one GPU's share (emb_peer.cuh)
+        em.emit("acc_ = emb::peer_all_sum(acc_, px, &emb_bcast);")
     em.emit(f"{em.var(state, 'f32')} = acc_;")
     em.block(tail, None)
-    shared = [f"    __shared__ float emb_slab[{max(comb.tree_len, 1)}];"]
-    source = finish(em, src, '#include "emb_reduce.cuh"', strict, shared, min_blocks)
+    shared = [f"    __shared__ float emb_slab[{max(comb.tree_len, 1)}];"] + (["    __shared__ float emb_bcast;"] if exchange else [])
+    source = finish(em, src, '#include "emb_reduce.cuh"' + ('\n#include "emb_peer.cuh"' if exchange else ""), strict, shared, min_blocks,
+                    ["emb::PeerExchange* px"] if exchange else [])
     how = "in the IR's own order" if strict else f"on {unroll * vec} independent accumulators per thread"
     how += f", {unroll} trips in flight per round"
     remarks = [f"block reduction template: {op} fold of {load.input} in {vec * 4}-byte ld.global.nc runs, {how}",
@@ -283,7 +287,23 @@ def match_reduce(src, strict: bool) -> Plan:
                (f", then the {comb.tree_len} warps' partials folded in the tree's order by every thread behind one barrier"
                 if comb.tree_len else "")]
     remarks += em.remarks
-    return Plan("reduce", source, remarks)
+    if exchange:
+        remarks.append("the result is a sum that ends the problem: given an exchange (the element range sharded over GPUs), the "
+                       "kernel itself stores its share into every peer's memory, waits (bounded) for theirs and adds them in rank order")
+    return Plan("reduce", source, remarks, extra_params=[dict(kind="exchange", name="px")] if exchange else [])
+
+
+def final_sum(src, op: str, comb, tail, state: str) -> bool:
+    """Is this the one-block kernel that ends a sum (meta.json: ``final``), storing the combined f32 state as the
+    problem's scalar result? Then its value may be one GPU's share of a sharded range, to be exchanged in place."""
+    meta = getattr(src, "meta", None) or {}
+    if not meta.get("final") or src.launch.grid != 1 or op != "add" or (comb.tree_op or "add") != "add" or comb.shuffle_op != "add":
+        return False
+    writes = [s for s in ir.walk(tail) if kind(s) == "Write"]
+    if len(writes) != 1 or tuple(writes[0].values) != (state,) or writes[0].atomic:
+        return False
+    out = src.buffers.get(writes[0].output)
+    return out is not None and out.dtype == "f32" and math.prod(out.shape or (1,)) == 1 and len(list(ir.walk(tail))) <= 2
 
 
 def has_cross(stmts) -> bool:

@@ -42,3 +42,71 @@ def combine_sum(partial, strict: bool = False, group=None):
         total += p
     partial.copy_(total)
     return partial
+
+
+MAX_PEERS = 8  # EMB_MAX_PEERS of csrc/templates/emb_peer.cuh
+RECORD_BYTES = 8 * MAX_PEERS * 2 + 16  # value pointers, flag pointers, rank, world, step, status
+
+
+def exchange_record(value_ptrs: list, rank: int, world: int) -> bytes:
+    """The bytes of ``emb::PeerExchange`` (csrc/templates/emb_peer.cuh) for this rank. ``value_ptrs[r]`` is the
+    address, as THIS rank sees it, of rank r's slot memory: ``float value[2][MAX_PEERS]`` followed by
+    ``unsigned flag[2][MAX_PEERS]``."""
+    import struct
+    if not 1 <= world <= MAX_PEERS or not 0 <= rank < world or len(value_ptrs) != world:
+        raise ValueError(f"an exchange of {world} ranks (at most {MAX_PEERS}), rank {rank}, {len(value_ptrs)} pointers")
+    pad = [0] * (MAX_PEERS - world)
+    flags = [p + 2 * MAX_PEERS * 4 for p in value_ptrs]
+    return struct.pack(f"<{2 * MAX_PEERS}Q4I", *value_ptrs, *pad, *flags, *pad, rank, world, 0, 0)
+
+
+SLOT_BYTES = 2 * MAX_PEERS * 4 * 2  # per rank: the value slots and the flag slots
+
+
+class PeerExchange:
+    """Symmetric slot memory of all ranks mapped into every rank, and the device record the sum's last kernel
+    takes (``emb::peer_all_sum``): the sharded array sum's one exchange step then happens inside that kernel,
+    by peer stores over NVLink and a bounded wait, instead of an all-reduce launched after it.
+
+    ``PeerExchange.create(group)`` allocates the slots through torch's symmetric memory and meets the other
+    ranks; ``PeerExchange.alone(device)`` is the one-rank form on ordinary device memory (the kernel then
+    exchanges with itself: the same code path, nothing to wait for)."""
+
+    def __init__(self, slots, value_ptrs: list, rank: int, world: int, keep=None):
+        import torch
+        self.slots, self.rank, self.world, self.keep = slots, rank, world, keep
+        raw = exchange_record(value_ptrs, rank, world)
+        self.record = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(slots.device)
+
+    @classmethod
+    def alone(cls, device):
+        import torch
+        slots = torch.zeros(SLOT_BYTES // 4, dtype=torch.float32, device=device)
+        return cls(slots, [slots.data_ptr()], 0, 1)
+
+    @classmethod
+    def create(cls, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        group = group or dist.group.WORLD
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        device = torch.device("cuda", torch.cuda.current_device())
+        slots = symm.empty(SLOT_BYTES // 4, dtype=torch.float32, device=device)
+        slots.zero_()
+        handle = symm.rendezvous(slots, group.group_name)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # every rank's slots are zero before any kernel stores into them
+        return cls(slots, [int(p) for p in handle.buffer_ptrs], rank, world, keep=handle)
+
+    def check(self) -> None:
+        """Raise if a kernel's wait for a peer gave up."""
+        from . import driver
+        words = self.record[-16:].cpu().view(dtype=__import__("torch").int32).tolist()
+        if words[3]:
+            raise driver.EmbError(-3, f"exchange: rank {words[0]} waited in vain for rank {words[3] - 1} at step {words[2] + 1}")
+
+    @property
+    def steps(self) -> int:
+        import torch
+        return int(self.record[-16:].cpu().view(dtype=torch.int32)[2])

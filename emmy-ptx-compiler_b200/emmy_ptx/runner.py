@@ -151,6 +151,8 @@ class CompiledKernel:
                     t = resolve(p["buffer"])
                     params.append(driver.TensorMap(t.data_ptr() + p.get("offset_bytes", 0), p["dtype"], p["dims"],
                                                    p["strides_bytes"], p["box"], p.get("swizzle", "128B")))
+                elif p["kind"] == "exchange":  # the device record of multi.PeerExchange, or null: no exchange
+                    params.append(tensors[EXCHANGE].data_ptr() if EXCHANGE in tensors else 0)
                 else:
                     raise ValueError(f"unknown parameter kind {p['kind']!r}")
             flags = driver.LAUNCH_PDL if li.get("pdl") else 0
@@ -163,10 +165,15 @@ class CompiledKernel:
         return out
 
 
-class Problem:
-    """A problem folder compiled in one mode and bound to tensors on one device."""
+EXCHANGE = "__exchange__"  # key of the exchange record among a problem's tensors (shared by all buffer sets)
 
-    def __init__(self, folder, mode: str = "optimized", device: int = 0, inputs: dict | None = None, scratch: dict | None = None):
+
+class Problem:
+    """A problem folder compiled in one mode and bound to tensors on one device. ``exchange`` (a multi.PeerExchange)
+    makes the last kernel of a sharded sum combine its scalar with the other ranks' inside the kernel."""
+
+    def __init__(self, folder, mode: str = "optimized", device: int = 0, inputs: dict | None = None, scratch: dict | None = None,
+                 exchange=None):
         import torch
         self.folder = Path(folder)
         self.meta = json.loads((self.folder / "meta.json").read_text())
@@ -194,6 +201,9 @@ class Problem:
                 else:
                     self.host[name] = given[name]
                     self.tensors[name] = to_torch(given[name], a["dtype"], self.device)
+        self.exchange = exchange
+        if exchange is not None:
+            self.tensors[EXCHANGE] = exchange.record
         self.launches = [l for k in self.kernels for l in k.bind(self.tensors)]
         self.sets = [self.launches]  # further copies of every buffer, for cold-cache timing (rotate())
         self.zero = [n for k in self.meta["kernels"] for n in k.get("zero_outputs", ())]
@@ -216,6 +226,8 @@ class Problem:
     def check_status(self) -> None:
         """Raise if a kernel's bounded wait gave up (its status word is non-zero)."""
         import torch
+        if self.exchange is not None:
+            self.exchange.check()
         for tensors in [self.tensors] + list(getattr(self, "copies", [])):
             for name, t in tensors.items():
                 if name.endswith(".status") and t.dtype == torch.int32:
@@ -238,11 +250,11 @@ class Problem:
     def rotate(self, min_bytes: int = 512 << 20, max_sets: int = 16) -> int:
         """Bind further copies of every tensor until the sets together hold ``min_bytes``:
         timing then walks the sets, so a run never finds its data in the 126 MB L2."""
-        per_set = sum(t.numel() * t.element_size() for t in self.tensors.values())
+        per_set = sum(t.numel() * t.element_size() for n, t in self.tensors.items() if n != EXCHANGE)
         want = max(2, min(max_sets, -(-min_bytes // max(per_set, 1))))
         self.copies = getattr(self, "copies", [])
         while len(self.sets) < want:
-            clone = {n: t.clone() for n, t in self.tensors.items()}
+            clone = {n: (t if n == EXCHANGE else t.clone()) for n, t in self.tensors.items()}
             self.copies.append(clone)
             self.sets.append([l for k in self.kernels for l in k.bind(clone)])
         return len(self.sets)

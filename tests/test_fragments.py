@@ -244,3 +244,46 @@ def test_one_warp_tile_added_atomically_twice():
     bufs = {"a": a, "bt": bt, "out": np.zeros((16, 8), np.float16)}
     fragment_oracle.run(one_warp_tile("f32", tail), bufs, 1, 32)
     assert np.allclose(bufs["out"].astype(np.float64), 2 * prod, rtol=5e-3, atol=5e-3)
+
+
+def attention_tile():
+    """One warp, one 16-query tile against 16 keys, entirely in fragments: S = Q K^T on two accumulators, the row
+    maximum and the row sum by FragmentRowReduce, exp(S - max) by FragmentApply with per-row operands, the weights
+    repacked into an A operand (FragmentRepack), O = P V, the division by the row sum, RegStore."""
+    from emmy_ptx.ir import (Axis, ElementwiseImpl, FragmentApply, FragmentRepack, FragmentRowReduce, LdmatrixLoad, MmaSyncPtx,
+                             RegFragment, RegStore, Tile, datatype)
+    L = problems.I
+    shape, f16, f32 = (16, 8, 16), datatype("f16"), datatype("f32")
+    body = [RegFragment(name="q", role="a", shape=shape, dtype=f16), RegFragment(name="kf", role="b", shape=shape, dtype=f16, count=2),
+            RegFragment(name="s", role="c", shape=shape, dtype=f32, count=2), RegFragment(name="p", role="a", shape=shape, dtype=f16),
+            RegFragment(name="vf", role="b", shape=shape, dtype=f16), RegFragment(name="o", role="c", shape=shape, dtype=f32),
+            LdmatrixLoad(frag="q", src_buffer="q", src_index=(L(0), L(0)), role="a", staged=False)]
+    for r in (0, 1):  # keys 8r .. 8r + 7: K is stored [key, d], the mma's column-major B as it stands
+        body += [LdmatrixLoad(frag=f"kf[{r}]", src_buffer="k", src_index=(L(8 * r), L(0)), role="b", staged=False, b_trans=True),
+                 MmaSyncPtx(c_frag=f"s[{r}]", a_frag="q", b_frag=f"kf[{r}]", shape=shape)]
+    body += [FragmentRowReduce(frags=("s[0]", "s[1]"), op=ElementwiseImpl("maximum"), top="m_top", bot="m_bot")]
+    body += [FragmentApply(out=f"s[{r}]", op=ElementwiseImpl("subtract"), args=(f"s[{r}]", ("m_top", "m_bot")), kinds=("frag", "row"),
+                           in_place=True, post=(ElementwiseImpl("exp"),)) for r in (0, 1)]
+    body += [FragmentRowReduce(frags=("s[0]", "s[1]"), op=ElementwiseImpl("add"), top="l_top", bot="l_bot"),
+             FragmentRepack(frag="p", srcs=("s[0]", "s[1]"), ab_dtype="f16"),
+             LdmatrixLoad(frag="vf", src_buffer="v", src_index=(L(0), L(0)), role="b", staged=False),  # V is [key, d]: K x N
+             MmaSyncPtx(c_frag="o", a_frag="p", b_frag="vf", shape=shape),
+             FragmentApply(out="o", op=ElementwiseImpl("divide"), args=("o", ("l_top", "l_bot")), kinds=("frag", "row"), in_place=True),
+             RegStore(dst_buffer="out", dst_index=(L(0), L(0)), frag="o", shape=shape)]
+    return (Tile(axes=(Axis(name="_lane", extent=32),), body=tuple(body), block_threads=32, aux_threads=0, raster_axes=None,
+                 raster_group=None, raster_orient="m"),)
+
+
+def attention_inputs():
+    rng = np.random.default_rng(5)
+    q, k, v = (rng.standard_normal(s).astype(np.float16) for s in ((16, 16), (16, 16), (16, 8)))
+    s = q.astype(np.float64) @ k.astype(np.float64).T
+    w = np.exp(s - s.max(1, keepdims=True))
+    return q, k, v, (w / w.sum(1, keepdims=True)) @ v.astype(np.float64)
+
+
+def test_attention_tile_in_fragments():
+    q, k, v, want = attention_inputs()
+    bufs = {"q": q, "k": k, "v": v, "out": np.zeros((16, 8), np.float32)}
+    fragment_oracle.run(attention_tile(), bufs, 1, 32)
+    assert np.allclose(bufs["out"], want, rtol=2e-3, atol=2e-3)  # the weights are rounded to f16 for the second mma

@@ -1,0 +1,47 @@
+"""The exchange step of the sharded array sum inside its last kernel (csrc/templates/emb_peer.cuh)."""
+
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from emmy_ptx import multi, problems, runner
+
+pytestmark = pytest.mark.gpu
+HERE = Path(__file__).resolve().parent
+
+
+def small_sum(tmp_path):
+    return problems.write(problems.array_sum(n=1 << 16, grid=16, block=256, ident="t_sum"), tmp_path)
+
+
+def test_one_rank_exchanges_with_itself(tmp_path):
+    """World of one: the kernel stores into its own slot, finds its own flag and returns its own value - the same
+    code path as with peers, with nothing to wait for; the step counter and both parities are walked."""
+    import torch
+    folder = small_sum(tmp_path)
+    want = runner.Problem(folder, "strict").run()["sum_1"]
+    ex = multi.PeerExchange.alone(torch.device("cuda", 0))
+    prob = runner.Problem(folder, "strict", exchange=ex)
+    assert any(p["kind"] == "exchange" for p in prob.kernels[-1].launch_info["params"])
+    for step in range(1, 4):
+        got = prob.run()["sum_1"]
+        assert got.tobytes() == want.tobytes()
+        assert ex.steps == step
+    prob.check_status()
+
+
+def test_ranks_on_several_gpus_agree_bit_for_bit(tmp_path):
+    import torch
+    n = min(torch.cuda.device_count(), 4)
+    if n < 2:
+        pytest.skip("needs two GPUs")
+    folder = small_sum(tmp_path)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+                        "--master-port", "29517", str(HERE / "exchange_worker.py"), str(folder), "6"],
+                       capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "exchange ok" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])

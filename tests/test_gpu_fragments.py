@@ -83,3 +83,17 @@ def test_one_warp_tile_added_atomically_twice():
     inputs, out = {"a": a, "bt": bt}, {"out": np.zeros((16, 8), np.float16)}
     got = runner.run_source(source("k_tile", one_warp_tile("f32", tail), inputs, out, 1, 32), {**inputs, **out}, "plain")["out"]
     assert np.allclose(got.astype(np.float64), 2 * prod, rtol=5e-3, atol=5e-3)
+
+
+@pytest.mark.parametrize("mode", ["optimized", "strict"])
+def test_attention_tile_in_fragments(mode):
+    """Row reductions across the four lanes of a row, per-row operands, exp, the repack of two accumulators into an A
+    operand: against the oracle's run of the same statements and the f64 softmax(Q K^T) V."""
+    from test_fragments import attention_inputs, attention_tile
+    q, k, v, want = attention_inputs()
+    inputs, out = {"q": q, "k": k, "v": v}, {"out": np.zeros((16, 8), np.float32)}
+    got = runner.run_source(source("k_tile", attention_tile(), inputs, out, 1, 32), {**inputs, **out}, mode)["out"]
+    ref = {**inputs, "out": np.zeros((16, 8), np.float32)}
+    fragment_oracle.run(attention_tile(), ref, 1, 32)
+    assert np.allclose(got, ref["out"], rtol=1e-3, atol=1e-3)
+    assert np.allclose(got, want, rtol=2e-3, atol=2e-3)

@@ -54,3 +54,23 @@ def test_two_ranks_combine_their_partial_sums(strict):
     x = np.random.default_rng(0).uniform(-1, 1, 1 << 16).astype(np.float32)
     a, b = x[:1 << 15].sum(dtype=np.float32), x[1 << 15:].sum(dtype=np.float32)
     assert results[0] == results[1] == float(np.float32(a + b))
+
+
+def test_exchange_record_layout():
+    """The bytes handed to the kernel as emb::PeerExchange: eight value pointers, eight flag pointers (each rank's flags
+    sit behind its 2 x 8 value slots), rank, world, step, status."""
+    import struct
+
+    from emmy_ptx import multi
+    raw = multi.exchange_record([0x10000, 0x20000, 0x30000], rank=2, world=3)
+    assert len(raw) == multi.RECORD_BYTES == 144
+    words = struct.unpack("<16Q4I", raw)
+    assert words[:3] == (0x10000, 0x20000, 0x30000) and words[3:8] == (0,) * 5
+    assert words[8:11] == (0x10040, 0x20040, 0x30040) and words[11:16] == (0,) * 5
+    assert words[16:] == (2, 3, 0, 0)
+    assert multi.SLOT_BYTES == 128
+    import pytest
+    with pytest.raises(ValueError):
+        multi.exchange_record([1] * 9, 0, 9)
+    with pytest.raises(ValueError):
+        multi.exchange_record([1, 2], 2, 2)
