@@ -44,6 +44,7 @@ __device__ __forceinline__ unsigned long long peer_ns() {
 // when there is no exchange). `bcast` is one float of shared memory.
 __device__ __forceinline__ float peer_all_sum(float mine, PeerExchange* px, float* bcast) {
     if (px == nullptr) return mine;
+    if (*static_cast<volatile unsigned*>(&px->status)) return mine;  // an earlier wait gave up: no further waiting, the host reports it
     __syncthreads();  // earlier uses of `bcast` are over
     if (threadIdx.x < 32) {
         const unsigned lane = threadIdx.x, world = px->world, rank = px->rank;
