@@ -45,22 +45,17 @@ def combine_sum(partial, strict: bool = False, group=None):
 
 
 MAX_PEERS = 8  # EMB_MAX_PEERS of csrc/templates/emb_peer.cuh
-RECORD_BYTES = 8 * MAX_PEERS * 2 + 16  # value pointers, flag pointers, rank, world, step, status
+RECORD_BYTES = 8 * MAX_PEERS + 16  # slot pointers, rank, world, step, status
+SLOT_BYTES = 2 * MAX_PEERS * 8  # per rank: u64 slot[2][MAX_PEERS]
 
 
-def exchange_record(value_ptrs: list, rank: int, world: int) -> bytes:
-    """The bytes of ``emb::PeerExchange`` (csrc/templates/emb_peer.cuh) for this rank. ``value_ptrs[r]`` is the
-    address, as THIS rank sees it, of rank r's slot memory: ``float value[2][MAX_PEERS]`` followed by
-    ``unsigned flag[2][MAX_PEERS]``."""
+def exchange_record(slot_ptrs: list, rank: int, world: int) -> bytes:
+    """The bytes of ``emb::PeerExchange`` (csrc/templates/emb_peer.cuh) for this rank. ``slot_ptrs[r]`` is the
+    address, as THIS rank sees it, of rank r's slot memory (``u64 slot[2][MAX_PEERS]``, zeroed)."""
     import struct
-    if not 1 <= world <= MAX_PEERS or not 0 <= rank < world or len(value_ptrs) != world:
-        raise ValueError(f"an exchange of {world} ranks (at most {MAX_PEERS}), rank {rank}, {len(value_ptrs)} pointers")
-    pad = [0] * (MAX_PEERS - world)
-    flags = [p + 2 * MAX_PEERS * 4 for p in value_ptrs]
-    return struct.pack(f"<{2 * MAX_PEERS}Q4I", *value_ptrs, *pad, *flags, *pad, rank, world, 0, 0)
-
-
-SLOT_BYTES = 2 * MAX_PEERS * 4 * 2  # per rank: the value slots and the flag slots
+    if not 1 <= world <= MAX_PEERS or not 0 <= rank < world or len(slot_ptrs) != world:
+        raise ValueError(f"an exchange of {world} ranks (at most {MAX_PEERS}), rank {rank}, {len(slot_ptrs)} pointers")
+    return struct.pack(f"<{MAX_PEERS}Q4I", *slot_ptrs, *([0] * (MAX_PEERS - world)), rank, world, 0, 0)
 
 
 class PeerExchange:
@@ -72,10 +67,10 @@ class PeerExchange:
     ranks; ``PeerExchange.alone(device)`` is the one-rank form on ordinary device memory (the kernel then
     exchanges with itself: the same code path, nothing to wait for)."""
 
-    def __init__(self, slots, value_ptrs: list, rank: int, world: int, keep=None):
+    def __init__(self, slots, slot_ptrs: list, rank: int, world: int, keep=None):
         import torch
         self.slots, self.rank, self.world, self.keep = slots, rank, world, keep
-        raw = exchange_record(value_ptrs, rank, world)
+        raw = exchange_record(slot_ptrs, rank, world)
         self.record = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(slots.device)
 
     @classmethod
