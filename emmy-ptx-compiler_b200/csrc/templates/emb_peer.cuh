@@ -22,9 +22,9 @@ struct PeerExchange {
     unsigned rank, world;
     unsigned step;    // steps completed by this rank (touched by this rank's kernels only)
     unsigned status;  // 0, or 1 + the peer whose value did not arrive in time (results are invalid from then on)
+    unsigned wait_limit_us;  // how long a wait for a peer may last (the host sets 2 s; a test of the time-out far less)
+    unsigned reserved;
 };
-
-constexpr unsigned long long PEER_WAIT_LIMIT_NS = 2000000000ull;
 
 __device__ __forceinline__ void peer_store(unsigned long long* p, unsigned long long v) {
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
@@ -56,9 +56,9 @@ __device__ __forceinline__ float peer_all_sum(float mine, PeerExchange* px, floa
             const unsigned long long* from = px->slot[rank] + parity + lane;
             unsigned long long got = peer_load(from);
             if (static_cast<unsigned>(got >> 32) != q) {
-                const unsigned long long t0 = peer_ns();
+                const unsigned long long t0 = peer_ns(), limit = 1000ull * px->wait_limit_us;
                 for (unsigned i = 1; static_cast<unsigned>((got = peer_load(from)) >> 32) != q; ++i) {
-                    if ((i & 63u) == 0 && peer_ns() - t0 > PEER_WAIT_LIMIT_NS) {
+                    if ((i & 63u) == 0 && peer_ns() - t0 > limit) {
                         atomicCAS(&px->status, 0u, lane + 1);
                         break;
                     }

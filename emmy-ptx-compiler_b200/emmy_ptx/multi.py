@@ -45,17 +45,18 @@ def combine_sum(partial, strict: bool = False, group=None):
 
 
 MAX_PEERS = 8  # EMB_MAX_PEERS of csrc/templates/emb_peer.cuh
-RECORD_BYTES = 8 * MAX_PEERS + 16  # slot pointers, rank, world, step, status
+RECORD_BYTES = 8 * MAX_PEERS + 24  # slot pointers, rank, world, step, status, wait limit (us), reserved
+WAIT_LIMIT_US = 2_000_000
 SLOT_BYTES = 2 * MAX_PEERS * 8  # per rank: u64 slot[2][MAX_PEERS]
 
 
-def exchange_record(slot_ptrs: list, rank: int, world: int) -> bytes:
+def exchange_record(slot_ptrs: list, rank: int, world: int, wait_limit_us: int = WAIT_LIMIT_US) -> bytes:
     """The bytes of ``emb::PeerExchange`` (csrc/templates/emb_peer.cuh) for this rank. ``slot_ptrs[r]`` is the
     address, as THIS rank sees it, of rank r's slot memory (``u64 slot[2][MAX_PEERS]``, zeroed)."""
     import struct
     if not 1 <= world <= MAX_PEERS or not 0 <= rank < world or len(slot_ptrs) != world:
         raise ValueError(f"an exchange of {world} ranks (at most {MAX_PEERS}), rank {rank}, {len(slot_ptrs)} pointers")
-    return struct.pack(f"<{MAX_PEERS}Q4I", *slot_ptrs, *([0] * (MAX_PEERS - world)), rank, world, 0, 0)
+    return struct.pack(f"<{MAX_PEERS}Q6I", *slot_ptrs, *([0] * (MAX_PEERS - world)), rank, world, 0, 0, int(wait_limit_us), 0)
 
 
 class PeerExchange:
@@ -67,10 +68,10 @@ class PeerExchange:
     ranks; ``PeerExchange.alone(device)`` is the one-rank form on ordinary device memory (the kernel then
     exchanges with itself: the same code path, nothing to wait for)."""
 
-    def __init__(self, slots, slot_ptrs: list, rank: int, world: int, keep=None):
+    def __init__(self, slots, slot_ptrs: list, rank: int, world: int, keep=None, wait_limit_us: int = WAIT_LIMIT_US):
         import torch
         self.slots, self.rank, self.world, self.keep = slots, rank, world, keep
-        raw = exchange_record(slot_ptrs, rank, world)
+        raw = exchange_record(slot_ptrs, rank, world, wait_limit_us)
         self.record = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(slots.device)
 
     @classmethod
@@ -94,14 +95,18 @@ class PeerExchange:
         dist.barrier(group)  # every rank's slots are zero before any kernel stores into them
         return cls(slots, [int(p) for p in handle.buffer_ptrs], rank, world, keep=handle)
 
+    def words(self) -> list:
+        """rank, world, steps completed, status (0, or 1 + the rank that was waited for in vain)."""
+        import torch
+        return self.record[8 * MAX_PEERS:8 * MAX_PEERS + 16].cpu().view(dtype=torch.int32).tolist()
+
     def check(self) -> None:
         """Raise if a kernel's wait for a peer gave up."""
         from . import driver
-        words = self.record[-16:].cpu().view(dtype=__import__("torch").int32).tolist()
+        words = self.words()
         if words[3]:
             raise driver.EmbError(-3, f"exchange: rank {words[0]} waited in vain for rank {words[3] - 1} at step {words[2] + 1}")
 
     @property
     def steps(self) -> int:
-        import torch
-        return int(self.record[-16:].cpu().view(dtype=torch.int32)[2])
+        return int(self.words()[2])

@@ -170,10 +170,15 @@ EXCHANGE = "__exchange__"  # key of the exchange record among a problem's tensor
 
 class Problem:
     """A problem folder compiled in one mode and bound to tensors on one device. ``exchange`` (a multi.PeerExchange)
-    makes the last kernel of a sharded sum combine its scalar with the other ranks' inside the kernel."""
+    makes the last kernel of a sharded sum combine its scalar with the other ranks' inside the kernel. ``canary``
+    puts every output and intermediate buffer between two guard zones and fills all of it with a poison pattern (NaN
+    for floats): ``check_canaries`` then shows a kernel that wrote outside its buffer, a NaN left in an output one that
+    did not write all of it (the stand-in for a memory checker on small shapes)."""
+
+    GUARD_BYTES = 4096
 
     def __init__(self, folder, mode: str = "optimized", device: int = 0, inputs: dict | None = None, scratch: dict | None = None,
-                 exchange=None):
+                 exchange=None, canary: bool = False):
         import torch
         self.folder = Path(folder)
         self.meta = json.loads((self.folder / "meta.json").read_text())
@@ -197,7 +202,11 @@ class Problem:
                     continue
                 if a.get("output") or a.get("intermediate"):
                     shape = a["shape"] or [1]
-                    self.tensors[name] = torch.zeros(shape, dtype=getattr(torch, TORCH_DTYPE[a["dtype"]]), device=self.device)
+                    dtype = getattr(torch, TORCH_DTYPE[a["dtype"]])
+                    if canary:
+                        self.tensors[name] = self._guarded(name, shape, dtype)
+                    else:
+                        self.tensors[name] = torch.zeros(shape, dtype=dtype, device=self.device)
                 else:
                     self.host[name] = given[name]
                     self.tensors[name] = to_torch(given[name], a["dtype"], self.device)
@@ -212,6 +221,30 @@ class Problem:
     def stream(self) -> int:
         import torch
         return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _guarded(self, name: str, shape, dtype):
+        import math
+
+        import torch
+        numel = math.prod(shape)
+        size = torch.empty(0, dtype=dtype).element_size()
+        pad = self.GUARD_BYTES // size
+        whole = torch.empty(numel + 2 * pad, dtype=dtype, device=self.device)
+        whole.view(torch.uint8).fill_(0xFF)  # NaN in every float format, -1 in the integer ones
+        self.guards = getattr(self, "guards", {})
+        self.guards[name] = (whole, pad, numel)
+        return whole[pad:pad + numel].view(shape)
+
+    def check_canaries(self) -> None:
+        """Raise if a guard zone around an output or intermediate buffer no longer holds the poison pattern."""
+        import torch
+        for name, (whole, pad, numel) in getattr(self, "guards", {}).items():
+            raw = whole.view(torch.uint8)
+            size = whole.element_size()
+            for zone, part in (("before", raw[:pad * size]), ("after", raw[(pad + numel) * size:])):
+                bad = (part != 0xFF).nonzero()
+                if bad.numel():
+                    raise driver.EmbError(-4, f"{name}: {bad.numel()} byte(s) written {zone} the buffer (first at byte {int(bad[0])} of the zone)")
 
     def run(self) -> dict:
         """Launch the chain once and return the final kernels' outputs as numpy arrays."""

@@ -34,6 +34,34 @@ def test_one_rank_exchanges_with_itself(tmp_path):
     prob.check_status()
 
 
+def test_a_wait_for_a_peer_that_never_stores_runs_out(tmp_path):
+    """Failure detection without a fault: a record that names a second rank whose slots nobody writes (ordinary memory
+    of this GPU). The kernel's wait for that rank gives up after the record's limit (20 ms here), the kernel ends
+    normally, the host reads which rank was missing; later steps return at once instead of waiting again."""
+    import time
+
+    import torch
+
+    from emmy_ptx import driver
+    folder = small_sum(tmp_path)
+    dev = torch.device("cuda", 0)
+    mine = torch.zeros(multi.SLOT_BYTES // 4, dtype=torch.float32, device=dev)
+    silent = torch.zeros(multi.SLOT_BYTES // 4, dtype=torch.float32, device=dev)
+    ex = multi.PeerExchange(mine, [mine.data_ptr(), silent.data_ptr()], rank=0, world=2, keep=silent, wait_limit_us=20_000)
+    prob = runner.Problem(folder, "optimized", exchange=ex)
+    t0 = time.perf_counter()
+    with pytest.raises(driver.EmbError, match="waited in vain for rank 1"):
+        prob.run()
+    assert time.perf_counter() - t0 < 5.0
+    assert ex.words() == [0, 2, 1, 2]  # the step is counted, rank 1 was waited for in vain
+    t0 = time.perf_counter()
+    for _ in range(50):
+        driver.launch(prob.launches, prob.stream)
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 0.5 and ex.steps == 1  # no more exchanges, no more waiting
+    assert torch.zeros(1, device=dev).item() == 0  # the context is alive
+
+
 def test_ranks_on_several_gpus_agree_bit_for_bit(tmp_path):
     import torch
     n = min(torch.cuda.device_count(), 4)

@@ -57,17 +57,17 @@ def test_two_ranks_combine_their_partial_sums(strict):
 
 
 def test_exchange_record_layout():
-    """The bytes handed to the kernel as emb::PeerExchange: eight slot pointers, rank, world, step, status."""
+    """The bytes handed to the kernel as emb::PeerExchange: eight slot pointers, rank, world, step, status, the wait limit."""
     import struct
 
     import pytest
 
     from emmy_ptx import multi
     raw = multi.exchange_record([0x10000, 0x20000, 0x30000], rank=2, world=3)
-    assert len(raw) == multi.RECORD_BYTES == 80
-    words = struct.unpack("<8Q4I", raw)
+    assert len(raw) == multi.RECORD_BYTES == 88
+    words = struct.unpack("<8Q6I", raw)
     assert words[:3] == (0x10000, 0x20000, 0x30000) and words[3:8] == (0,) * 5
-    assert words[8:] == (2, 3, 0, 0)
+    assert words[8:] == (2, 3, 0, 0, multi.WAIT_LIMIT_US, 0)
     assert multi.SLOT_BYTES == 128
     with pytest.raises(ValueError):
         multi.exchange_record([1] * 9, 0, 9)
