@@ -224,7 +224,7 @@ def main() -> None:
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.families is None:
-        args.families = "sum,matmul,attention,mlp" if world == 1 else "sum"
+        args.families = "sum,matmul,fragments,attention,mlp" if world == 1 else "sum"
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the kernels run on the GPU only")
     torch.cuda.set_device(local)
