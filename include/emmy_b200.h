@@ -150,6 +150,30 @@ int emb_tensor_map(void* map_out, const void* base, int dtype, int rank, const u
 #define EMB_STATIC_SUM_MAX_BLOCKS 2048
 int emb_array_sum_f32_static(const float* x, uint64_t n, uint32_t blocks, float* sum_out, void* stream);
 
+/* ---- the exchange record of a sharded sum ------------------------------------
+ * No counterpart in the reference, whose problems run on one GPU. A module whose
+ * launch header lists a parameter of kind "exchange" (the last kernel of a sum)
+ * takes there a DEVICE pointer to this record, or NULL for no exchange. With a
+ * record the kernel stores its f32 result, with the step number in the upper half
+ * of one 8-byte word, into slot [step & 1][rank] of every rank's slot memory
+ * (peer stores), waits at most wait_limit_us for every rank's word of the same
+ * step in its own slot memory and returns the sum of all ranks' values in rank
+ * order. slot[r] is rank r's slot memory as THIS rank addresses it: 2 x
+ * EMB_MAX_PEERS 8-byte words, zeroed before the first launch and mapped into
+ * every rank (CUDA IPC or fabric handles; torch's symmetric memory does it). All
+ * ranks must run the same number of such launches. status != 0 after a launch:
+ * rank status - 1 was waited for in vain, that result and all later ones are
+ * invalid, and no later launch waits again. */
+#define EMB_MAX_PEERS 8
+typedef struct {
+    uint64_t slot[EMB_MAX_PEERS]; /* device addresses, unused entries 0 */
+    uint32_t rank, world;         /* this rank, number of ranks (1..EMB_MAX_PEERS) */
+    uint32_t step;                /* steps completed; start at 0, the kernels count */
+    uint32_t status;              /* start at 0 */
+    uint32_t wait_limit_us;       /* e.g. 2000000 */
+    uint32_t reserved;            /* 0 */
+} emb_peer_exchange_t;
+
 /* Text of the last error on the calling thread ("" if none). */
 const char* emb_last_error(void);
 

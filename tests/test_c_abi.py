@@ -47,3 +47,30 @@ def test_product_path_refuses_to_run_without_a_gpu(tmp_path):
     folder = problems.write(problems.array_sum(n=4096, grid=4, block=128, final_block=64, ident="t"), tmp_path)
     with pytest.raises(driver.EmbError):
         runner.Problem(folder)
+
+
+def test_exchange_record_of_the_header_is_what_the_host_packs(tmp_path):
+    """emb_peer_exchange_t (C, include/emmy_b200.h), emb::PeerExchange (the kernels' view) and multi.exchange_record
+    (the bytes the host writes) describe the same 88 bytes."""
+    import subprocess
+
+    from emmy_ptx import multi
+    src = tmp_path / "layout.cpp"
+    src.write_text('''
+#include <cstddef>
+#include <cstdio>
+#include "emmy_b200.h"
+#include "emb_peer.cuh"
+int main() {
+    std::printf("%zu %zu %zu %zu %zu %zu\\n", sizeof(emb_peer_exchange_t), offsetof(emb_peer_exchange_t, rank),
+                offsetof(emb_peer_exchange_t, step), offsetof(emb_peer_exchange_t, status),
+                offsetof(emb_peer_exchange_t, wait_limit_us), sizeof(emb::PeerExchange));
+    return !(offsetof(emb::PeerExchange, status) == offsetof(emb_peer_exchange_t, status) &&
+             offsetof(emb::PeerExchange, wait_limit_us) == offsetof(emb_peer_exchange_t, wait_limit_us));
+}
+''')
+    exe = tmp_path / "layout"
+    templates = ROOT / "emmy-ptx-compiler_b200" / "csrc" / "templates"
+    subprocess.run(["nvcc", "-x", "cu", "-I", str(ROOT / "include"), "-I", str(templates), "-o", str(exe), str(src)], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()
+    assert [int(v) for v in out] == [multi.RECORD_BYTES, 64, 72, 76, 80, multi.RECORD_BYTES]
