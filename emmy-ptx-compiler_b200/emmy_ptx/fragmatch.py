@@ -303,6 +303,7 @@ class Trace:
                 self.b_layouts = self.b_layouts - {layout}
         need(cols is not None and self.b_layouts, "a B operand whose k does not run with A's")
         state = self.acc[(cname, ci)]
+        need(state != "stored", "an accumulator that is summed into again after it was stored")
         if state is None:
             self.acc[(cname, ci)] = dict(rows=rows, cols=cols, ks=[ks], a=a_id, b=b_id)
         else:
@@ -317,7 +318,7 @@ class Trace:
         need(s.dst_buffer in self.src.buffers and s.dst_buffer not in self.smem, "a RegStore into shared memory")
         cname, ci = self.member(s.frag)
         state = self.acc.get((cname, ci))
-        need(state is not None, "a stored accumulator that no mma wrote")
+        need(state is not None and state != "stored", "a stored accumulator that no mma wrote, or one stored twice")
         shape = self.src.buffers[s.dst_buffer].shape
         ldm = int(s.ldm) or (math.prod(shape[s.row_dim + 1:]) if s.row_dim is not None else int(shape[-1]))
         ldn = math.prod(shape[s.col_dim + 1:]) if s.col_dim is not None else 1

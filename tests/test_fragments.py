@@ -158,6 +158,12 @@ def test_the_proof_refuses_what_is_not_the_product(tmp_path):
     guarded = partial_source(tmp_path, m=40, n=60, k=72, splits=1, staged=False)
     assert "a block axis in the gmem_guard" in refusal(guarded)
 
+    # the last fragment stored a second time
+    tile = src.body[0]
+    again = frontend.KernelSource(src.name, (tile.replace(body=tile.body + (tile.body[-1],)),), src.params, src.buffers, src.launch,
+                                  src.written, src.constants, src.meta, src.path)
+    assert "stored twice" in refusal(again)
+
     # a block axis inside a quotient
     def divide(s):
         if ir.kind(s) == "RegStore":
