@@ -229,7 +229,9 @@ def main() -> None:
         raise SystemExit("bench.py: no CUDA device; the kernels run on the GPU only")
     torch.cuda.set_device(local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import datetime
+        # a rank that dies must end the others' next collective within minutes, not NCCL's default ten
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(minutes=4))
     warmup = max(args.warmup, 3)
     pk, pk_kind = peaks()
 
@@ -252,6 +254,10 @@ def main() -> None:
                     how = f"NCCL all-reduce after the kernel (symmetric memory unavailable: {type(e).__name__}: {e})"[:240]
             else:
                 how = "NCCL all-reduce after the kernel (--exchange nccl)"
+            agreed = torch.tensor([0 if exchange is None else 1], device="cuda")
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)  # all ranks take the same route
+            if exchange is not None and int(agreed.item()) == 0:
+                exchange, how = None, "NCCL all-reduce after the kernel (symmetric memory unavailable on another rank)"
         prob = runner.Problem(PKG / "problems" / w["folder"], args.mode, device=local, exchange=exchange)
         stream = prob.stream
         if args.buffer_sets == 1:
