@@ -621,6 +621,14 @@ class Emitter(fragcode.FragmentStatements):
             else:
                 self.emit(f"{target} = {value};")
 
+    def s_ZeroPrologue(self, s) -> None:
+        """CTA 0 zeroes ``words`` 32-bit words of another kernel's accumulator (emmy_ptx/lower.py:1240-1259 of the reference)."""
+        arr, _, _, shared, _ = self.memory(s.dst)
+        if shared:
+            raise CodegenError("ZeroPrologue of a shared array")
+        self.emit(f"if (blockIdx.x == 0) for (long long z_ = threadIdx.x; z_ < {int(s.words)}LL; z_ += {self.src.launch.block}) "
+                  f"reinterpret_cast<unsigned*>({arr})[z_] = 0u;")
+
     # ------------------------------------------------------------ cross-thread statements
 
     def x_Sync(self, s, guard) -> None:

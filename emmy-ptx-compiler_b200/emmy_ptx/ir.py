@@ -347,13 +347,19 @@ class FragmentPromote(Node):
     _fields = (("dst", _MISSING), ("src", _MISSING))
 
 
+class ZeroPrologue(Node):
+    """CTA 0 zeroes ``words`` 32-bit words of ``dst``, another kernel's accumulator (emmy_ptx/lower.py:1240-1259)."""
+    _fields = (("dst", _MISSING), ("words", _MISSING))
+
+
 FRAGMENT_FORM = ("CpAsyncCopy", "CpAsyncCommit", "CpAsyncWait", "RegFragment", "LdmatrixLoad", "MmaSyncPtx", "RegStore",
                  "FragmentApply", "FragmentRowReduce", "FragmentRepack", "FragmentPromote")
+KNOWN["ZeroPrologue"] = ZeroPrologue
 for _cls in (CpAsyncCopy, CpAsyncCommit, CpAsyncWait, RegFragment, LdmatrixLoad, MmaSyncPtx, RegStore, FragmentApply,
              FragmentRowReduce, FragmentRepack, FragmentPromote):
     KNOWN[_cls.__name__] = _cls
 # read and printed like the rest, taken by no lowering here
-for _name in ("ZeroPrologue", "FuncCallExpr", "Builtin", "FlatIndex", "FragmentLayout", "Epilogue"):
+for _name in ("FuncCallExpr", "Builtin", "FlatIndex", "FragmentLayout", "Epilogue"):
     KNOWN[_name] = type(_name, (Node,), {})
 
 

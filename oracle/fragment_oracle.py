@@ -357,6 +357,11 @@ class _FragmentBlocks(_Blocks):
             else:
                 mem[where] = out[ok]
 
+    def do_ZeroPrologue(self, s, mask):  # lower.py:1240-1259: CTA 0 zeroes 32-bit words of another kernel's accumulator
+        if (self.ctaid == 0).any():
+            flat = self.globals[s.dst].reshape(-1)
+            flat.view(np.uint8)[:4 * int(s.words)] = 0
+
     def do_Smem(self, s, mask):
         if s.name not in self.shared:
             ctype = getattr(s, "dtype", None) or "float"

@@ -293,3 +293,19 @@ def test_attention_tile_in_fragments():
     bufs = {"q": q, "k": k, "v": v, "out": np.zeros((16, 8), np.float32)}
     fragment_oracle.run(attention_tile(), bufs, 1, 32)
     assert np.allclose(bufs["out"], want, rtol=2e-3, atol=2e-3)  # the weights are rounded to f16 for the second mma
+
+
+def zero_prologue_kernel(words: int):
+    """CTA 0 zeroes the first ``words`` 32-bit words of ``acc``; every thread then adds 1 to acc[thread % 8] atomically."""
+    from emmy_ptx.ir import Axis, Let, Literal, Tile, Write, ZeroPrologue, datatype
+    P, L, V = problems.B, problems.I, problems.V
+    return (Tile(axes=(Axis(name="a0", extent=64),), body=(
+        ZeroPrologue(dst="acc", words=words), Let(name="one", value=Literal(value=1.0, dtype="float"), dtype=datatype("f32")),
+        Write(output="tally", index=(P("%", V("a0"), L(8)),), values=("one",), value_dtype=None, atomic=True)),
+        block_threads=64, aux_threads=0, raster_axes=None, raster_group=None, raster_orient="m"),)
+
+
+def test_zero_prologue_clears_another_kernels_accumulator():
+    bufs = {"acc": np.full(40, 7.0, np.float32), "tally": np.zeros(8, np.float32)}
+    fragment_oracle.run(zero_prologue_kernel(33), bufs, 1, 64)
+    assert (bufs["acc"][:33] == 0).all() and (bufs["acc"][33:] == 7.0).all() and (bufs["tally"] == 8).all()

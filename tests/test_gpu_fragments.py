@@ -97,3 +97,11 @@ def test_attention_tile_in_fragments(mode):
     fragment_oracle.run(attention_tile(), ref, 1, 32)
     assert np.allclose(got, ref["out"], rtol=1e-3, atol=1e-3)
     assert np.allclose(got, want, rtol=2e-3, atol=2e-3)
+
+
+def test_zero_prologue_clears_another_kernels_accumulator():
+    from test_fragments import zero_prologue_kernel
+    arrays = {"acc": np.full(40, 7.0, np.float32), "tally": np.zeros(8, np.float32)}
+    src = source("k_zero", zero_prologue_kernel(33), {}, arrays, 1, 64)
+    got = runner.run_source(src, arrays, "optimized")
+    assert (got["acc"][:33] == 0).all() and (got["acc"][33:] == 7.0).all() and (got["tally"] == 8).all()
