@@ -74,6 +74,26 @@ __device__ __forceinline__ float from_f8e4m3(unsigned code) {
     return __half2float(__ushort_as_half(static_cast<unsigned short>(halves & 0xffffu)));
 }
 
+// the other three fp8 conversions of the reference (emmy_ptx/elementwise.py:100-129): e5m2 decoded the same way
+// (infinities and NaNs stay); encodes round to nearest even and saturate to the largest finite value, NaN to 0x7f
+// (one cvt.rn.satfinite on the pair (x, x), low byte kept)
+__device__ __forceinline__ float from_f8e5m2(unsigned code) {
+    unsigned short pair = static_cast<unsigned short>(code & 0xffu);
+    unsigned halves;
+    asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(halves) : "h"(pair));
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(halves & 0xffffu)));
+}
+__device__ __forceinline__ unsigned char to_f8e4m3(float x) {
+    unsigned short pair;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %1;" : "=h"(pair) : "f"(x));
+    return static_cast<unsigned char>(pair & 0xffu);
+}
+__device__ __forceinline__ unsigned char to_f8e5m2(float x) {
+    unsigned short pair;
+    asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %1;" : "=h"(pair) : "f"(x));
+    return static_cast<unsigned char>(pair & 0xffu);
+}
+
 // reduction combines as types, for the templates
 struct OpAdd {
     static __device__ __forceinline__ float apply(float a, float b) { return add(a, b); }

@@ -226,14 +226,19 @@ class Emitter(fragcode.FragmentStatements):
         if op in COMPARE:
             (a, da), (b, db) = args
             return self.convert(f"({self.to_float(a, da)} {COMPARE[op]} {self.to_float(b, db)})", "i32", out)
+        if op in ("to_f8e4m3", "to_f8e5m2"):  # the result is the byte code, whatever 8-bit type carries it
+            code = f"emb::{op}({self.convert(args[0][0], args[0][1], 'f32')})"
+            return code if out in ("f8e4m3", "f8e5m2", "u8") else self.convert(code, "u8", out)
+        if out in ("f8e4m3", "f8e5m2"):
+            raise CodegenError(f"{op} with an fp8 result")
         work = "f32" if out in ("f16", "bf16") else out  # halves are computed in float and rounded once
         T = CTYPE[work]
         c = [self.convert(code, dt, work) for code, dt in args]
         if op == "where":
             cond = f"({self.to_float(args[0][0], args[0][1])} != 0)"
             r = f"({cond} ? {c[1]} : {c[2]})"
-        elif op == "from_f8e4m3":
-            r = self.convert(f"emb::from_f8e4m3((unsigned){args[0][0]})", "f32", work)
+        elif op in ("from_f8e4m3", "from_f8e5m2"):
+            r = self.convert(f"emb::{op}((unsigned){args[0][0]})", "f32", work)
         elif work in ("f32", "f64"):
             suffix = "f" if work == "f32" else ""
             table = {

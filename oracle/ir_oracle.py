@@ -57,6 +57,7 @@ NP = {"f32": np.float32, "f64": np.float64, "f16": np.float16, "i16": np.int16, 
       "u8": np.uint8, "u16": np.uint16, "u32": np.uint32, "u64": np.uint64, "bool": np.bool_}
 if ml_dtypes is not None:
     NP["bf16"] = ml_dtypes.bfloat16  # extension (see the module text)
+NP["f8e4m3"] = NP["f8e5m2"] = np.uint8  # extension: fp8 values travel as their byte codes
 _NAME_OF = {np.dtype(v): k for k, v in NP.items()}
 # C type names an Smem declaration may carry (tests/oracle.py:36)
 C_TYPES = {"float": "f32", "double": "f64", "int": "i32", "unsigned": "u32", "unsigned int": "u32", "__half": "f16",
@@ -488,6 +489,33 @@ def _decode_e4m3(t, code):
     return byte.view(ml_dtypes.float8_e4m3fn).astype(np.float32).astype(t)
 
 
+_F8 = {"e4m3": ("float8_e4m3fn", 448.0), "e5m2": ("float8_e5m2", 57344.0)}
+
+
+def _decode_f8(fmt):
+    """Extension: ``from_f8<fmt>``, a byte code to its value, exactly (emmy_ptx/elementwise.py:100-110: e4m3's 0x7f / 0xff are
+    NaN, e5m2's infinities and NaNs stay)."""
+    def fn(t, code):
+        if ml_dtypes is None:
+            raise Unsupported("the fp8 operations need ml_dtypes")
+        byte = (np.asarray(code).astype(np.int64) & 0xFF).astype(np.uint8)
+        return byte.view(getattr(ml_dtypes, _F8[fmt][0])).astype(np.float32).astype(t)
+    return fn
+
+
+def _encode_f8(fmt):
+    """Extension: ``to_f8<fmt>``, f32 to a byte code: round to nearest even, saturate to the largest finite value
+    (infinities too), NaN to 0x7f (emmy_ptx/elementwise.py:113-123, one ``cvt.rn.satfinite``)."""
+    def fn(t, x):
+        if ml_dtypes is None:
+            raise Unsupported("the fp8 operations need ml_dtypes")
+        name, largest = _F8[fmt]
+        x = np.asarray(x).astype(np.float32)
+        codes = np.clip(x, -largest, largest).astype(getattr(ml_dtypes, name)).view(np.uint8)
+        return np.where(np.isnan(x), np.uint8(0x7F), codes).astype(np.uint8)
+    return fn
+
+
 def _cast_then(fn):
     """A unary computed in the result type: convert the operand first, then apply ``fn``."""
     return lambda t, x: fn(x.astype(t), t)
@@ -510,6 +538,8 @@ _UNARY.update({name: _in_double(fn) for name, fn in {
 }.items()})
 _UNARY["bitwise_count"] = lambda t, x: np.bitwise_count(x).astype(t)
 _UNARY["from_f8e4m3"] = _decode_e4m3  # extension
+_UNARY["from_f8e5m2"] = _decode_f8("e5m2")  # extension
+_UNARY["to_f8e4m3"], _UNARY["to_f8e5m2"] = _encode_f8("e4m3"), _encode_f8("e5m2")  # extensions
 
 # two-operand operations (tests/oracle.py:323-328), computed on operands converted to the result type
 _BINARY = dict(add=np.add, subtract=np.subtract, multiply=np.multiply, divide=np.divide, maximum=fmax, minimum=fmin,
