@@ -76,6 +76,13 @@ def c_float(v: float, dtype: str = "f32") -> str:
     return text + ("f" if dtype != "f64" else "")
 
 
+def divisor_constant(name) -> bool:
+    """Is ``name`` a ConstantOp emmy made for the divisor of a source division: a scalar argument of a ``div`` node
+    (``<node>_c<k>``) or a mean's element count (``<out>_count``)? (emmy_ptx/lower.py:1598-1604 of the reference)"""
+    import re
+    return bool(name) and (re.fullmatch(r"(div|divide|true_divide|truediv)(_\d+)?_c\d+", name) is not None or name.endswith("_count"))
+
+
 def has_cross_thread(stmts) -> bool:
     return any(kind(s) in CROSS_THREAD for s in ir.walk(stmts))
 
@@ -99,6 +106,8 @@ def divisible(e, k: int, facts: dict) -> bool:
 
 class Emitter(fragcode.FragmentStatements):
     def __init__(self, src, plain: bool = False, strict: bool = False):
+        self.const_from: dict = {}  # IR name -> the compile-time constant buffer it was loaded from
+        self.reciprocal_of: dict = {}  # IR name -> value of the source divisor it is the reciprocal of
         self.frags: dict = {}  # fragment name -> (role, element dtype, members, registers)
         self.frag_decls: list = []
         self.smem_align: dict = {}
@@ -533,7 +542,36 @@ class Emitter(fragcode.FragmentStatements):
     def s_Assign(self, s) -> None:
         args = [self.use(a) for a in s.args]
         out = dtype_name(s.dtype) or promote(s.op.name, [dt for _, dt in args])
+        quotient = self.constant_quotient(s, out)
+        self.reciprocal_of.pop(s.name, None)
+        self.const_from.pop(s.name, None)
+        if s.op.name == "reciprocal" and len(s.args) == 1 and divisor_constant(self.const_from.get(s.args[0])):
+            self.reciprocal_of[s.name] = float(self.src.constants[self.const_from[s.args[0]]])
+        if quotient is not None:
+            (x, dx), c = quotient
+            self.emit(f"{self.var(s.name, out)} = {self.convert(f'__fdiv_rn({self.convert(x, dx, 'f32')}, {c_float(c)})', 'f32', out)};")
+            self.remark("x * reciprocal(c), where emmy split the source's x / c, computed as the correctly rounded x / c "
+                        "(the divisor is a ConstantOp of a division)")
+            return
         self.emit(f"{self.var(s.name, out)} = {self.apply(s.op.name, args, out)};")
+
+    def constant_quotient(self, s, out: str):
+        """((x code, x dtype), c) when the Assign multiplies x by the reciprocal of a source divisor c outside every loop
+        with an f32 or f16 result: emmy turns the source's ``x / c`` into ``x * reciprocal(c)``, which can be an ulp from
+        the correctly rounded quotient numpy gives (pointwise problems compare at rtol = 0). Recognised, as in the
+        reference (emmy_ptx/lower.py:898-930,1598-1604), by the NAME of the constant (``div_c1``, ``*_count``): a
+        convention, not a proof. Not under --strict or --plain, not for a power-of-two c (its reciprocal is exact)."""
+        if (s.op.name != "multiply" or len(s.args) != 2 or self.strict or self.plain or self.loop_depth or out not in ("f32", "f16")
+                or "quotient" in getattr(self, "disable", ())):
+            return None
+        for i in (0, 1):
+            c = self.reciprocal_of.get(s.args[i])
+            if c is None or c == 0.0 or not math.isfinite(c):
+                continue
+            if math.frexp(c)[0] in (0.5, -0.5):
+                return None
+            return self.use(s.args[1 - i]), c
+        return None
 
     def s_Accum(self, s) -> None:
         if s.name not in self.vars:
@@ -582,6 +620,9 @@ class Emitter(fragcode.FragmentStatements):
         vdt = self.value_dtype(dt)
         out = dtype_name(s.dtype) or vdt
         n = len(s.names)
+        for name in s.names:  # what these names held is gone
+            self.const_from.pop(name, None)
+            self.reciprocal_of.pop(name, None)
         if (not self.plain and not shared and readonly and n in (2, 4) and dt == "f32" and out == "f32"
                 and self.aligned(shape, s.index, n)):
             vec = f"float{n}"
@@ -592,6 +633,8 @@ class Emitter(fragcode.FragmentStatements):
             self.emit("}")
             self.remark(f"{n * 4}-byte global load of {s.input}")
             return
+        if len(s.names) == 1 and s.input in getattr(self.src, "constants", {}):
+            self.const_from[s.names[0]] = s.input
         for k, name in enumerate(s.names):
             elem = f"{arr}[{idx} + {k}]" if k else f"{arr}[{idx}]"
             if not shared and readonly and dt in ("f32", "f64", "i32", "u32", "i64", "u64", "u8", "i8", "i16", "u16"):

@@ -17,10 +17,10 @@ def dtype_name(a: np.ndarray) -> str:
     return DTYPE_NAME[a.dtype]
 
 
-def source(name, body, inputs: dict, outputs: dict, grid: int, block: int) -> KernelSource:
+def source(name, body, inputs: dict, outputs: dict, grid: int, block: int, constants: dict | None = None) -> KernelSource:
     buffers = {n: Buffer(n, tuple(a.shape), dtype_name(a)) for n, a in {**inputs, **outputs}.items()}
     return KernelSource(name, tuple(body), tuple(inputs) + tuple(outputs), buffers, Launch(grid, block, 0),
-                        frozenset(outputs))
+                        frozenset(outputs), constants=dict(constants or {}))
 
 
 def same_bits(got, want) -> bool:
