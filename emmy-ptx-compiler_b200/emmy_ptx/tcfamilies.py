@@ -37,11 +37,12 @@ GEMM_PAIR_MIN_TILES = 74  # CTA pairs (256 x 256 tiles) only when they give ever
 ATTN_POLY_PERIOD = 4  # every n-th pair of softmax weights gets its 2^x from an FMA polynomial instead of the SFU (0: none)
 
 
-def wrapper(src, includes: str, body: list, extra_sig: list, threads: int, min_blocks: int = 1) -> str:
+def wrapper(src, includes: str, body: list, extra_sig: list, threads: int, min_blocks: int = 1, cluster: int = 1) -> str:
     sig = codegen.signature(src)
     sig = ", ".join([sig] + extra_sig) if extra_sig else sig
+    attrs = f"__cluster_dims__({cluster}, 1, 1) " if cluster > 1 else ""  # the module itself asks for the cluster (.reqnctapercluster)
     head = [includes,
-            f'extern "C" __global__ void __launch_bounds__({threads}, {min_blocks}) {src.name}({sig}) {{']
+            f'extern "C" __global__ void {attrs}__launch_bounds__({threads}, {min_blocks}) {src.name}({sig}) {{']
     return "\n".join(head + codegen.pdl_prologue(src, True) + body + ["}"]) + "\n"
 
 
@@ -135,7 +136,7 @@ def match_matmul(src, strict: bool) -> Plan:
             f"emb::GemmShape{{{M}, {N}, {K}}}, status);"]
     extra_sig = ["const __grid_constant__ CUtensorMap tmap_a", "const __grid_constant__ CUtensorMap tmap_b",
                  "unsigned* __restrict__ status"]
-    source = wrapper(src, '#include "emb_gemm.cuh"', call, extra_sig, 192)
+    source = wrapper(src, '#include "emb_gemm.cuh"', call, extra_sig, 192, cluster=g["cluster"])
     extra = [tmap("a", a.input, A.dtype, (K, M), (K * 2,), (64, 128)),
              tmap("b", b.input, B.dtype, (K, N), (K * 2,), (64, g["b_rows"])),
              dict(kind="status", name="status")]

@@ -125,3 +125,27 @@ def test_meta_wins_over_the_ir_and_is_optional(folder, tmp_path, capsys):
     src = frontend.load(lone)
     assert "deriving parameters and launch from the IR" in capsys.readouterr().err
     assert src.params == ("x", "sum__partial") and src.launch.block == 128 and src.launch.grid == 4
+
+
+def test_one_wave_hint_and_cluster_request_are_in_the_module(tmp_path):
+    """`.minnctapersm 1` iff the grid fits in one wave of the 148 SMs (reference emmy_ptx/lower.py:104-106, with its
+    TARGET_SMS of another GPU), switched off by EMMY_PTX_DISABLE=hint; a kernel on CTA pairs asks for its cluster."""
+    import os
+    import subprocess
+    import sys
+    problems_dir = ROOT / "emmy-ptx-compiler_b200" / "problems"
+
+    def compile_(ir, **env):
+        r = subprocess.run([sys.executable, str(ROOT / "compile.py"), "--report", str(ir)], capture_output=True, text=True,
+                           env={**os.environ, **env})
+        assert r.returncode == 0, r.stderr
+        return r.stdout, r.stderr
+
+    ptx, report = compile_(problems_dir / "r_sum_16m" / "k_sum_1_reduce.ir.json")  # one block
+    assert ".minnctapersm 1" in ptx and ".minnctapersm 1 (the grid fits in one wave)" in report
+    ptx, report = compile_(problems_dir / "r_sum_16m" / "k_sum_1_reduce.ir.json", EMMY_PTX_DISABLE="hint")
+    assert ".minnctapersm" not in ptx and "one wave" not in report
+    ptx, report = compile_(problems_dir / "f_softmax_8192x4096" / "k_softmax_reduce.ir.json")  # 8192 blocks
+    assert "one wave" not in report
+    ptx, report = compile_(problems_dir / "m_f16_8192" / "k_matmul.ir.json")
+    assert ".reqnctapercluster 2, 1, 1" in ptx and ".reqnctapercluster 2" in report
