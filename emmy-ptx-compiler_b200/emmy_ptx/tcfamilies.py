@@ -24,7 +24,6 @@ from __future__ import annotations
 import math
 
 from . import codegen
-from .codegen import CTYPE
 from .families import Plan, Refusal, is_var, need, single_tile
 from .ir import dtype_name, kind
 

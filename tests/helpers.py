@@ -4,7 +4,6 @@ from __future__ import annotations
 
 import numpy as np
 
-from emmy_ptx import ir
 from emmy_ptx.frontend import Buffer, KernelSource, Launch
 
 DTYPE_NAME = {np.dtype(np.float32): "f32", np.dtype(np.float64): "f64", np.dtype(np.float16): "f16",

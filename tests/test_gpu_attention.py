@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 from emmy_ptx import problems, runner
-from helpers import margin, oracle_problem
+from helpers import oracle_problem
 
 pytestmark = pytest.mark.gpu
 RTOL = 2e-3

@@ -3,7 +3,6 @@ says) and the tcgen05 template the proved schedules go to, against the oracle's 
 reference's expected values."""
 
 import json
-from pathlib import Path
 
 import numpy as np
 import pytest

@@ -71,7 +71,6 @@ def test_matmul_strict_and_plain_keep_the_ir_order(tmp_path):
 
 
 def test_matmul_full_size_sampled_cells_and_properties():
-    import torch
     folder = Path(runner.__file__).resolve().parent.parent / "problems" / "m_f16_8192"
     prob = runner.Problem(folder, "optimized")
     got = prob.run()["matmul"]
