@@ -73,3 +73,52 @@ def test_exchange_record_layout():
         multi.exchange_record([1] * 9, 0, 9)
     with pytest.raises(ValueError):
         multi.exchange_record([1, 2], 2, 2)
+
+
+def test_exchange_protocol_with_ranks_as_threads():
+    """The slot protocol of csrc/templates/emb_peer.cuh restated on host memory, ranks as threads that run at random
+    speeds: one (step, value) word per (parity, sender) slot in every rank's memory; a rank stores its word into all
+    ranks' slots of parity step & 1, waits for every sender's word of that step in its own slots, and adds in rank order.
+    Every rank must see the same sums for many steps, although a fast rank may already be writing the next step (other
+    parity) while a slow one still reads: it can never be two steps ahead, because its wait of the step between needs
+    the slow rank's word, which is stored only after the slow rank has read the older values."""
+    import random
+    import threading
+    import time
+
+    world, steps = 4, 300
+    slots = [[[(0, 0.0)] * world for _ in range(2)] for _ in range(world)]  # slots[owner][parity][sender] = (step, value)
+    results = [[] for _ in range(world)]
+    failed = []
+
+    def rank_main(rank: int) -> None:
+        rng = random.Random(rank)
+        for q in range(1, steps + 1):
+            mine = float(np.float32(rank + 1) * np.float32(q))
+            if rng.random() < 0.2:
+                time.sleep(rng.random() * 0.002)
+            for owner in range(world):
+                slots[owner][q & 1][rank] = (q, mine)
+            got = []
+            for sender in range(world):
+                deadline = time.time() + 5.0
+                while slots[rank][q & 1][sender][0] != q:
+                    if time.time() > deadline:
+                        failed.append((rank, q, sender))
+                        return
+                    time.sleep(0)
+                got.append(slots[rank][q & 1][sender][1])
+            total = np.float32(got[0])
+            for v in got[1:]:
+                total = np.float32(total + np.float32(v))
+            results[rank].append(float(total))
+
+    threads = [threading.Thread(target=rank_main, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(60)
+    assert not failed, failed
+    want = [float(np.float32(sum(range(1, world + 1))) * np.float32(q)) for q in range(1, steps + 1)]
+    for r in range(world):
+        assert results[r] == want
