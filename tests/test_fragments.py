@@ -309,3 +309,32 @@ def test_zero_prologue_clears_another_kernels_accumulator():
     bufs = {"acc": np.full(40, 7.0, np.float32), "tally": np.zeros(8, np.float32)}
     fragment_oracle.run(zero_prologue_kernel(33), bufs, 1, 64)
     assert (bufs["acc"][:33] == 0).all() and (bufs["acc"][33:] == 7.0).all() and (bufs["tally"] == 8).all()
+
+
+def epilogue_tile():
+    """The one-warp tile stored through a fused epilogue with row and column guards: y = relu(acc) + (row of the element
+    in the tile), bound as the reference binds it (the fragment's element under the epilogue's parameter name, emmy's
+    __M__ / __N__ for the element's coordinates; emmy_ptx/tensorcore.py:432-452). Rows >= 13 and columns >= 6 are not
+    stored."""
+    from emmy_ptx.ir import Assign, KNOWN, Let, RegStore, datatype
+    L, V = problems.I, problems.V
+    f32 = datatype("f32")
+    epilogue = KNOWN["Epilogue"](params=("e0",), results=("y",), body=(
+        Assign(name="r", op="relu", args=("e0",), dtype=None), Let(name="mrow", value=V("__M__"), dtype=f32),
+        Assign(name="y", op="add", args=("r", "mrow"), dtype=None)))
+    tail = (RegStore(dst_buffer="out", dst_index=(L(0), L(0)), frag="acc", shape=(16, 8, 16), epilogue=epilogue,
+                     m_guard=(L(0), L(13)), n_guard=(L(0), L(6))),)
+    return one_warp_tile("f32", tail)
+
+
+def epilogue_expected(prod):
+    rows, cols = np.indices((16, 8))
+    want = np.maximum(prod, 0) + rows
+    return np.where((rows < 13) & (cols < 6), want, -7.0)
+
+
+def test_regstore_epilogue_and_guards():
+    a, bt, prod, _ = tile_inputs()
+    bufs = {"a": a, "bt": bt, "out": np.full((16, 8), -7.0, np.float32)}
+    fragment_oracle.run(epilogue_tile(), bufs, 1, 32)
+    assert np.allclose(bufs["out"], epilogue_expected(prod), rtol=1e-3, atol=1e-3)

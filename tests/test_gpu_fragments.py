@@ -104,3 +104,11 @@ def test_zero_prologue_clears_another_kernels_accumulator():
     src = source("k_zero", zero_prologue_kernel(33), {}, arrays, 1, 64)
     got = runner.run_source(src, arrays, "optimized")
     assert (got["acc"][:33] == 0).all() and (got["acc"][33:] == 7.0).all() and (got["tally"] == 8).all()
+
+
+def test_regstore_epilogue_and_guards():
+    from test_fragments import epilogue_expected, epilogue_tile
+    a, bt, prod, _ = tile_inputs()
+    inputs, out = {"a": a, "bt": bt}, {"out": np.full((16, 8), -7.0, np.float32)}
+    got = runner.run_source(source("k_tile", epilogue_tile(), inputs, out, 1, 32), {**inputs, **out}, "optimized")["out"]
+    assert np.allclose(got, epilogue_expected(prod), rtol=1e-3, atol=1e-3)
