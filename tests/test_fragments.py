@@ -338,3 +338,38 @@ def test_regstore_epilogue_and_guards():
     bufs = {"a": a, "bt": bt, "out": np.full((16, 8), -7.0, np.float32)}
     fragment_oracle.run(epilogue_tile(), bufs, 1, 32)
     assert np.allclose(bufs["out"], epilogue_expected(prod), rtol=1e-3, atol=1e-3)
+
+
+def kn_tile():
+    """One warp, B kept K x N (16 x 8) in shared memory and read with ldmatrix .x2.trans (the single-fragment form of
+    the K x N slab), A read straight from global memory."""
+    from emmy_ptx.ir import Axis, LdmatrixLoad, Load, MmaSyncPtx, RegFragment, RegStore, Smem, Sync, Tile, Write, datatype
+    P, L, V = problems.B, problems.I, problems.V
+    lane, shape, f16 = V("_lane"), (16, 8, 16), datatype("f16")
+    fill = []
+    for j in range(4):  # lane l stages row l / 2, columns (l % 2) * 4 + j of the 16 x 8 slab
+        at = (P("/", lane, L(2)), P("+", P("*", P("%", lane, L(2)), L(4)), L(j)))
+        fill += [Load(names=(f"b{j}",), input="b", index=at, dtype=None), Write(output="b_s", index=at, values=(f"b{j}",), value_dtype=None)]
+    return (Tile(axes=(Axis(name="_lane", extent=32),), body=(
+        Smem(name="b_s", extents=(16, 8), dtype="__half", align=16), *fill, Sync(barrier_id=0, count=None, warp=False),
+        RegFragment(name="fa", role="a", shape=shape, dtype=f16), RegFragment(name="fb", role="b", shape=shape, dtype=f16),
+        RegFragment(name="acc", role="c", shape=shape, dtype=datatype("f32")),
+        LdmatrixLoad(frag="fa", src_buffer="a", src_index=(L(0), L(0)), role="a", staged=False),
+        LdmatrixLoad(frag="fb", src_buffer="b_s", src_index=(L(0), L(0)), role="b", ldm=8, b_trans=False),
+        MmaSyncPtx(c_frag="acc", a_frag="fa", b_frag="fb", shape=shape),
+        RegStore(dst_buffer="out", dst_index=(L(0), L(0)), frag="acc", shape=shape)),
+        block_threads=32, aux_threads=0, raster_axes=None, raster_group=None, raster_orient="m"),)
+
+
+def kn_inputs():
+    rng = np.random.default_rng(17)
+    a = (rng.standard_normal((16, 16)) / 4).astype(np.float16)
+    b = (rng.standard_normal((16, 8)) / 4).astype(np.float16)
+    return a, b, a.astype(np.float64) @ b.astype(np.float64)
+
+
+def test_b_read_transposed_from_a_k_by_n_slab():
+    a, b, want = kn_inputs()
+    bufs = {"a": a, "b": b, "out": np.zeros((16, 8), np.float32)}
+    fragment_oracle.run(kn_tile(), bufs, 1, 32)
+    assert np.allclose(bufs["out"], want, rtol=1e-5, atol=1e-5)

@@ -112,3 +112,11 @@ def test_regstore_epilogue_and_guards():
     inputs, out = {"a": a, "bt": bt}, {"out": np.full((16, 8), -7.0, np.float32)}
     got = runner.run_source(source("k_tile", epilogue_tile(), inputs, out, 1, 32), {**inputs, **out}, "optimized")["out"]
     assert np.allclose(got, epilogue_expected(prod), rtol=1e-3, atol=1e-3)
+
+
+def test_b_read_transposed_from_a_k_by_n_slab():
+    from test_fragments import kn_inputs, kn_tile
+    a, b, want = kn_inputs()
+    inputs, out = {"a": a, "b": b}, {"out": np.zeros((16, 8), np.float32)}
+    got = runner.run_source(source("k_tile", kn_tile(), inputs, out, 1, 32), {**inputs, **out}, "plain")["out"]
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-5)
