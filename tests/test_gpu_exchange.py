@@ -63,9 +63,9 @@ def test_a_wait_for_a_peer_that_never_stores_runs_out(tmp_path):
 
 def test_ranks_on_several_gpus_agree_bit_for_bit(tmp_path):
     import torch
-    n = min(torch.cuda.device_count(), 4)
-    if n < 2:
+    if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
+    n = 2
     folder = small_sum(tmp_path)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
