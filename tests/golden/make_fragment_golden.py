@@ -1,7 +1,7 @@
 """Generate tests/golden/m_f16_128/: the reference's shipped fragment-form example as fixture data.
 
 Run in the build container only (it reads the reference checkout, which does not travel):
-``python tests/golden/make_fragment_golden.py [path-to-reference]``.
+``python tests/golden/make_fragment_golden.py <path-to-reference>``.
 
 examples/m_f16_128 is the one kernel chain the reference ships in emmy's tensor-core (fragment) form: a
 split-K matmul on mma.sync fragments fed by cp.async (k_matmul__partial) and the fold of its two slabs
@@ -53,4 +53,6 @@ def main(ref: Path) -> None:
 
 
 if __name__ == "__main__":
-    main(Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference"))
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_fragment_golden.py <path to the reference checkout>")
+    main(Path(sys.argv[1]))

@@ -1,7 +1,7 @@
 """Generate tests/golden/oracle_cases.{json,npz}: outputs of the REFERENCE's own interpreter.
 
 Run in the build container only (it reads the reference checkout, which does
-not travel): ``python tests/golden/make_golden.py [path-to-reference]``.
+not travel): ``python tests/golden/make_golden.py <path-to-reference>``.
 
 The reference's tests/oracle.py is imported unchanged. It needs three symbols
 of the absent emmy-ml package; a stand-in provides them from the reference's own
@@ -280,7 +280,9 @@ def shipped_examples(ref: Path):
 
 
 def main():
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to the reference checkout>")
+    ref = Path(sys.argv[1])
     oracle = reference_oracle(ref)
     cases, arrays = [], {}
 
