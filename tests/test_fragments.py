@@ -373,3 +373,24 @@ def test_b_read_transposed_from_a_k_by_n_slab():
     bufs = {"a": a, "b": b, "out": np.zeros((16, 8), np.float32)}
     fragment_oracle.run(kn_tile(), bufs, 1, 32)
     assert np.allclose(bufs["out"], want, rtol=1e-5, atol=1e-5)
+
+
+def test_the_proof_over_a_grid_of_shapes(tmp_path):
+    """Every staged schedule the generator writes is a matmul: the proof must accept it exactly when the template's own
+    limits allow (result of at least 8192 cells, K slabs of whole 64s when there are several), and name the shapes."""
+    import itertools
+    for m, n, k, splits, layout, dtype in itertools.product((32, 128, 272), (64, 160), (128, 384), (1, 2), ("kn", "nk"), ("f16", "bf16")):
+        if (m % 16) or (n % 32) or ((k // splits) % 32) or (layout == "kn" and dtype == "bf16" and m == 32):
+            continue
+        src = partial_source(tmp_path, m=m, n=n, k=k, splits=splits, b_layout=layout, dtype=dtype)
+        fits = m * n >= 8192 and (splits == 1 or (k // splits) % 64 == 0)
+        try:
+            plan = fragmatch.match_fragment_matmul(src, False)
+        except families.Refusal as r:
+            assert not fits, (m, n, k, splits, layout, dtype, str(r))
+            assert "too small" in str(r) or "multiples of 64" in str(r)
+            continue
+        assert fits, (m, n, k, splits, layout, dtype)
+        assert f"x0 [{m} x {k}]" in plan.remarks[0] and f"N = {n}]" in plan.remarks[0]
+        assert ("K x N" if layout == "kn" else "N x K") in plan.remarks[0]
+        assert f"emb::GemmShape{{{m}, {n}, {k}, {splits}}}" in plan.source
