@@ -1,6 +1,6 @@
 """TEST INFRASTRUCTURE, NOT PRODUCT: the oracle extended to emmy's tensor-core (fragment) form.
 
-Only the tests may import this module; no product code path may.
+Only the tests and the CPU-baseline legs of ``bench.py`` may import this module; no product code path may.
 
 The reference's interpreter (tests/oracle.py) refuses the fragment statements, so its own check of a
 fragment-form kernel is the example's ``expected.npz`` alone (examples/m_f16_128). What is restated here
