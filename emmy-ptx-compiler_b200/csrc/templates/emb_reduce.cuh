@@ -69,15 +69,21 @@ template <class Op, int LEN> __device__ __forceinline__ float tree_fold(const fl
     return s[0];
 }
 
-// Per-thread fold of x[i + j], j < VEC, for i = start, start + step, ... < end.
+// What a fold does to a loaded value before folding it; the default folds the value itself.
+struct MapIdentity {
+    __device__ __forceinline__ float operator()(float v) const { return v; }
+};
+
+// Per-thread fold of map(x[i + j]), j < VEC, for i = start, start + step, ... < end.
 //
 // The trips are taken UNROLL at a time with every load of the round issued before the first
 // add (a thread keeps UNROLL * VEC * 4 bytes in flight); trips past `end` are predicated off, so
 // a ragged last round costs no serial tail. STRICT: one accumulator, the IR's order (a skipped
 // trip adds nothing, not even a zero). Otherwise UNROLL * VEC independent accumulators, merged
 // at the end.
-template <int VEC, class Fold, int UNROLL, bool STRICT>
-__device__ __forceinline__ float strided_fold(const float* __restrict__ x, long long start, long long step, long long end) {
+template <int VEC, class Fold, int UNROLL, bool STRICT, class Map = MapIdentity>
+__device__ __forceinline__ float strided_fold(const float* __restrict__ x, long long start, long long step, long long end,
+                                              Map map = Map()) {
     float a[STRICT ? 1 : UNROLL][STRICT ? 1 : VEC];
 #pragma unroll
     for (int u = 0; u < (STRICT ? 1 : UNROLL); ++u)
@@ -97,7 +103,7 @@ __device__ __forceinline__ float strided_fold(const float* __restrict__ x, long 
 #pragma unroll
                 for (int j = 0; j < VEC; ++j) {
                     float& acc = a[STRICT ? 0 : u][STRICT ? 0 : j];
-                    acc = Fold::apply(acc, v[u].v[j]);
+                    acc = Fold::apply(acc, map(v[u].v[j]));
                 }
             }
     }

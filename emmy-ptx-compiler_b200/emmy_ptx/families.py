@@ -189,10 +189,10 @@ def tile_decode(em: Emitter, tile, block: int) -> None:
         stride *= n
 
 
-def finish(em: Emitter, src, includes: str, strict: bool, shared: list, min_blocks=None, extra_sig=()) -> str:
+def finish(em: Emitter, src, includes: str, strict: bool, shared: list, min_blocks=None, extra_sig=(), block=None) -> str:
     decls = [f"    {CTYPE[dt]} v_{n} = emb::zero<{CTYPE[dt]}>();" for n, dt in em.vars.items() if n not in ("lane", "warp")]
     head = [f"#define EMB_STRICT {int(strict)}", includes, codegen.PRELUDE.split("\n", 1)[1],
-            f'extern "C" __global__ void __launch_bounds__({src.launch.block}{f", {min_blocks}" if min_blocks else ""}) '
+            f'extern "C" __global__ void __launch_bounds__({block or src.launch.block}{f", {min_blocks}" if min_blocks else ""}) '
             f'{src.name}({", ".join([codegen.signature(src), *extra_sig])}) {{',
             "    int v_lane = threadIdx.x & 31, v_warp = threadIdx.x >> 5;", "    (void)v_lane; (void)v_warp;",
             "    const unsigned emb_warp = 0xffffffffu; (void)emb_warp;"] + codegen.pdl_prologue(src, True)
@@ -202,59 +202,269 @@ def finish(em: Emitter, src, includes: str, strict: bool, shared: list, min_bloc
 # ---------------------------------------------------------------- block reduction
 
 
-def match_reduce(src, strict: bool) -> Plan:
+@dataclass
+class FoldCopy:
+    """One copy of a fold's body: Load x[.., loop variable + offset]; Assign*; Accum(state, value)."""
+    load: object
+    offset: int
+    chain: list
+    accum: object
+
+
+def index_offset(e, var: str):
+    """k when the expression is ``var`` or ``var + k`` / ``k + var`` for an integer literal k, else None."""
+    if is_var(e, var):
+        return 0
+    if kind(e) == "BinaryExpr" and e.op == "+":
+        if is_var(e.left, var) and is_int(e.right):
+            return e.right.value
+        if is_var(e.right, var) and is_int(e.left):
+            return e.left.value
+    return None
+
+
+def fold_copies(loop) -> list:
+    """The loop body as copies of Load (one name), Assigns, Accum; raises Refusal when it is anything else."""
+    copies, cur = [], None
+    var = loop.axis.name
+    for st in loop.body:
+        k = kind(st)
+        if k == "Load":
+            need(cur is None, "a Load before the previous value was folded")
+            need(len(st.names) == 1 and st.index, "the fold's Load is not of one value")
+            off = index_offset(st.index[-1], var)
+            need(off is not None, "the load is not indexed by the loop variable (plus a constant)")
+            cur = FoldCopy(st, off, [], None)
+        elif k == "Assign":
+            need(cur is not None, "arithmetic before the fold's Load")
+            cur.chain.append(st)
+        elif k == "Accum":
+            need(cur is not None, "an Accum without a loaded value")
+            cur.accum = st
+            copies.append(cur)
+            cur = None
+        else:
+            raise Refusal(f"a {k} inside the fold")
+    need(cur is None and copies, "the fold does not end with an Accum")
+    return copies
+
+
+def thread_varying(pre, t_axis: str, src) -> set:
+    """Names bound before the fold whose value may differ between the threads of a block: whatever reads the thread
+    axis, lane or warp, a buffer the kernel writes, or another such name. (The other Tile axes are the same in all
+    threads of a block, the thread axis being the innermost; a name never bound reads as zero everywhere.)"""
+    varying = {t_axis, "lane", "warp"}
+    for st in pre:
+        k = kind(st)
+        if k == "Let":
+            reads, names = ir.expr_vars(st.value), (st.name,)
+        elif k == "Assign":
+            reads, names = set(st.args), (st.name,)
+        elif k == "Load":
+            reads = set().union(*[ir.expr_vars(e) for e in st.index]) if st.index else set()
+            names = tuple(st.names)
+            if st.input in src.written or st.input not in src.buffers:
+                reads = reads | {t_axis}
+        else:
+            continue
+        if reads & varying:
+            varying.update(names)
+        else:
+            varying.difference_update(names)
+    return varying
+
+
+def regroup_refusal(src, tile, pre, loop, copies, merges, comb, tail, t_axis: str, block: int, op: str):
+    """Why the cooperating threads of the block may NOT take 16-byte chunks ``4 t + 4 B k + j`` instead of their
+    stride ``t + B k`` (None: they may). The reference's conditions, over this module's own analysis:
+    shape (emmy_ptx/regroup.py:187-233): the loop starts at the thread's rank, steps by copies * B, has no end
+    expression, 4 B divides its extent, copy j reads the loop variable plus j B, every copy computes alike;
+    combine (emmy_ptx/regroup.py:75-147): the partials flow only into combines with the loop's own fold - the
+    copies' merges, the butterfly over the block's lanes, the tree over its warps - and are not read otherwise;
+    ownership (emmy_ptx/lower.py:250-272): nothing the body reads from outside differs between the threads, no
+    outer index moves with the thread, the loads read memory the kernel does not write."""
+    B, R, var = block, len(copies), loop.axis.name
+    extent = loop.axis.extent.as_static()
+    if not is_var(loop.start, t_axis):
+        return "the loop does not start at each thread's own rank among the block's threads"
+    if not is_int(loop.step, R * B):
+        return f"the step is not {R} cop{'y' if R == 1 else 'ies'} x {B} threads"
+    if loop.end is not None:
+        return "the loop has an end expression"
+    if extent % (4 * B) or extent < 4 * B:
+        return f"{4 * B} (four elements for each of the {B} threads) does not divide the extent {extent}"
+    if sorted(c.offset for c in copies) != [j * B for j in range(R)]:
+        return "the copies do not read the loop variable plus 0, B, 2 B, ..."
+    first = min(copies, key=lambda c: c.offset)
+    varying = thread_varying(pre, t_axis, src)
+    bound_anywhere = {c.load.names[0] for c in copies} | {a.name for c in copies for a in c.chain}
+    states = {c.accum.name for c in copies}
+    for c in copies:
+        ld = c.load
+        buf = src.buffers.get(ld.input)
+        if buf is None or ld.input in src.written:
+            return f"it reads {ld.input}, which the kernel also writes"
+        if ld.input != first.load.input or len(ld.index) != len(first.load.index) or any(
+                not same_expr(a, b, {}) for a, b in zip(ld.index[:-1], first.load.index[:-1])):
+            return "the copies read different rows"
+        for e in ld.index[:-1]:
+            if {var, t_axis, "lane", "warp"} & ir.expr_vars(e):
+                return "an outer index moves with the loop or with the thread (an element would take its new thread's row)"
+        rename = {ld.names[0]: first.load.names[0]}
+        if len(c.chain) != len(first.chain):
+            return "the copies do not compute alike"
+        for a, b in zip(c.chain, first.chain):
+            if a.op.name != b.op.name or dtype_name(a.dtype) != dtype_name(b.dtype) or len(a.args) != len(b.args):
+                return "the copies do not compute alike"
+            for x, y in zip(a.args, b.args):
+                if x in states or x == var:
+                    return "the body reads an accumulator or the loop variable's value"
+                if x in bound_anywhere:
+                    if rename.get(x) != y:
+                        return "the copies do not compute alike"
+                elif x != y:
+                    return "the copies do not compute alike"
+                elif x in varying:
+                    return f"{x} may differ between the cooperating threads (an element would take its new thread's)"
+            rename[a.name] = b.name
+        acc = c.accum
+        if CANON.get(acc.op.name) != op or acc.base is not None or dtype_name(acc.dtype) not in (None, "f32"):
+            return "a copy folds with another operation or type"
+        if rename.get(acc.value) != (first.accum.value if first.accum.value in bound_anywhere else None):
+            return "the copies do not fold the value they computed alike"
+    if len(states) != R and len(states) != 1:
+        return "the copies share some accumulators and not others"
+    live = first.accum.name if len(states) == 1 else None
+    merged = set()
+    for m in merges:
+        if CANON.get(m.op.name) != op:
+            return f"{m.value} is folded into {m.name} with {m.op.name}, but the loop folds it with {op}"
+        merged.add(m.value)
+        live = m.name
+    if len(states) > 1 and (live is None or merged | {live} != states or live in merged):
+        return "the copies' partials are not all folded into one before the butterfly"
+    if comb.state != (live or first.accum.name):
+        return "the butterfly does not combine the loop's partial"
+    if comb.shuffle_op != op:
+        return f"the butterfly combines with {comb.shuffle_op}, but the loop folds with {op}"
+    if comb.tree_op is not None and comb.tree_op != op:
+        return f"the tree combines with {comb.tree_op}, but the loop folds with {op}"
+    for st in ir.walk(tail):
+        reads = set(getattr(st, "args", ()) or ()) | set(getattr(st, "values", ()) or ())
+        if reads & merged:
+            return "a partial folded away is still read"
+    return None
+
+
+def match_reduce(src, strict: bool, disable=frozenset()) -> Plan:
     tile = single_tile(src)
     block = src.launch.block
     t_axis = thread_axis(tile, block)
     body = list(tile.body)
-    need(body and kind(body[0]) == "StridedLoop", "the Tile does not start with a strided fold")
-    loop = body[0]
+    at = 0
+    while at < len(body) and kind(body[at]) in ("Let", "Load", "Assign"):
+        at += 1
+    pre = body[:at]
+    need(at < len(body) and kind(body[at]) == "StridedLoop", "the Tile does not start with a strided fold")
+    need(all(kind(s) != "Load" or (len(s.names) == 1 and s.input not in src.written) for s in pre),
+         "a Load before the fold that is not one read-only value")
+    loop = body[at]
     need(loop.seed and not has_cross(loop.body), "the fold is not seeded or holds cross-thread statements")
     need(loop.body and kind(loop.body[0]) == "Load", "the fold's first statement is not a Load")
-    load = loop.body[0]
-    vec = len(load.names)
+    vec = len(loop.body[0].names)
     need(vec in (1, 2, 4), "a load of 3 or more than 4 names")
-    accs = loop.body[1:]
-    need(len(accs) == vec and all(kind(a) == "Accum" for a in accs), "the fold is not one Accum per loaded value")
-    state = accs[0].name
-    op = CANON.get(accs[0].op.name)
-    need(op in OP_TYPE, f"no template for a fold with {accs[0].op.name}")
-    for a, name in zip(accs, load.names):
-        need(a.name == state and a.value == name and a.base is None and CANON.get(a.op.name) == op
-             and dtype_name(a.dtype) in (None, "f32"), "the Accums do not fold the loaded values, in order, into one f32 state")
-    need(state not in load.names, "the state is overwritten by the load")
-
-    em = Emitter(src, plain=False, strict=strict)
-    em.depth = 1
-    tile_decode(em, tile, block)
     var = loop.axis.name
-    pointer, row = row_pointer(em, src, load, var)
     extent = loop.axis.extent.as_static()
-    need(extent <= row, "the loop runs past the buffer's row")
-    em.facts[var] = (loop.start, loop.step)
+    regrouped, merges, copies = False, [], None
     if vec > 1:
-        need(divisible(loop.start, vec, em.facts) and divisible(loop.step, vec, em.facts) and extent % vec == 0
-             and row % vec == 0 and (loop.end is None or divisible(loop.end, vec, em.facts)),
-             f"the {vec * 4}-byte runs are not provably aligned")
-    (start, ks), (step, kt) = em.expr(loop.start), em.expr(loop.step)
-    need(ks == "int" and kt == "int", "a float loop bound")
-    end = f"{extent}LL"
-    if loop.end is not None:
-        end_code, ke = em.expr(loop.end)
-        need(ke == "int", "a float loop bound")
-        end = end_code
-
-    comb = match_combine(body, 1, state, block)
-    tail = body[1 + comb.consumed:]
+        # the run is spelled in the IR: Load of `vec` names, one Accum per name into one state, in order
+        load = loop.body[0]
+        accs = loop.body[1:]
+        need(len(accs) == vec and all(kind(a) == "Accum" for a in accs), "the fold is not one Accum per loaded value")
+        state = accs[0].name
+        op = CANON.get(accs[0].op.name)
+        need(op in OP_TYPE, f"no template for a fold with {accs[0].op.name}")
+        for a, name in zip(accs, load.names):
+            need(a.name == state and a.value == name and a.base is None and CANON.get(a.op.name) == op
+                 and dtype_name(a.dtype) in (None, "f32"), "the Accums do not fold the loaded values, in order, into one f32 state")
+        need(state not in load.names, "the state is overwritten by the load")
+        need(not pre, "statements before a fold of multi-name loads")
+        chain, value = [], None
+    else:
+        copies = fold_copies(loop)
+        op = CANON.get(copies[0].accum.op.name)
+        need(op in OP_TYPE, f"no template for a fold with {copies[0].accum.op.name}")
+        load = min(copies, key=lambda c: c.offset).load
+    pos = at + 1
+    if copies is not None:
+        states = {c.accum.name for c in copies}
+        while pos < len(body) and kind(body[pos]) == "Accum" and body[pos].base is None and body[pos].name in states \
+                and body[pos].value in states and body[pos].name != body[pos].value:
+            merges.append(body[pos])
+            pos += 1
+        state = merges[-1].name if merges else copies[0].accum.name
+    comb = match_combine(body, pos, state, block)
+    tail = body[pos + comb.consumed:]
     need(not has_cross(tail), "cross-thread statements after the tree")
     slabs = {s.name for s in body if kind(s) == "Smem"}
     need(not slab_read_later(tail, slabs), "the slab is read after the tree")
     for s in ir.walk(tail):
         need(kind(s) in ("Cond", "Write", "Assign", "Let", "Load"), f"a {kind(s)} after the tree")
 
-    trips = None
-    if is_int(loop.step) and loop.end is None and loop.step.value > 0:
-        trips = -(-extent // loop.step.value)  # the most trips any thread takes
+    remarks = []
+    if copies is not None:
+        why = None
+        if strict:
+            why = "--strict keeps the IR's order of additions"
+        elif "regroup" in disable:
+            why = "disabled"
+        else:
+            why = regroup_refusal(src, tile, pre, loop, copies, merges, comb, tail, t_axis, block, op)
+        if why is None:
+            regrouped = True
+        else:
+            if not strict:
+                remarks.append(f"loop {var}: kept strided, not regrouped: {why}")
+            c0 = copies[0]
+            need(len(copies) == 1 and not merges and c0.offset == 0,
+                 f"an unrolled fold that is not regrouped: {why} (the statement lowering keeps its copies)")
+            need(c0.accum.base is None and dtype_name(c0.accum.dtype) in (None, "f32"), "the Accum is not a plain f32 fold")
+            need(c0.accum.name not in {a for st in c0.chain for a in st.args} and var not in {a for st in c0.chain for a in st.args},
+                 "the body reads its accumulator or the loop variable's value")
+        first = min(copies, key=lambda c: c.offset)
+        chain, value = first.chain, first.accum.value
+        need(all(dtype_name(a.dtype) in (None, "f32") for a in chain), "arithmetic in the fold that is not f32")
+        need(value == first.load.names[0] or value in {a.name for a in chain}, "the Accum does not fold a value of the body")
+
+    em = Emitter(src, plain=False, strict=strict)
+    em.depth = 1
+    tile_decode(em, tile, block)
+    em.block(pre, None)
+    pointer, row = row_pointer(em, src, load, var)
+    need(extent <= row, "the loop runs past the buffer's row")
+    if regrouped:
+        B4 = 4 * block
+        need(row % 4 == 0, "the row length is not a multiple of the 16-byte run")
+        run, start, step, end = 4, f"(long long)v_{t_axis} * 4LL", f"{B4}LL", f"{extent}LL"
+        trips = extent // B4
+    else:
+        run = vec
+        em.facts[var] = (loop.start, loop.step)
+        if vec > 1:
+            need(divisible(loop.start, vec, em.facts) and divisible(loop.step, vec, em.facts) and extent % vec == 0
+                 and row % vec == 0 and (loop.end is None or divisible(loop.end, vec, em.facts)),
+                 f"the {vec * 4}-byte runs are not provably aligned")
+        (start, ks), (step, kt) = em.expr(loop.start), em.expr(loop.step)
+        need(ks == "int" and kt == "int", "a float loop bound")
+        end = f"{extent}LL"
+        if loop.end is not None:
+            end_code, ke = em.expr(loop.end)
+            need(ke == "int", "a float loop bound")
+            end = end_code
+        trips = None
+        if is_int(loop.step) and loop.end is None and loop.step.value > 0:
+            trips = -(-extent // loop.step.value)  # the most trips any thread takes
+
     if REDUCE_UNROLL is not None:
         unroll = REDUCE_UNROLL
     elif trips is not None and trips <= MAX_FULL_UNROLL:
@@ -265,11 +475,26 @@ def match_reduce(src, strict: bool) -> Plan:
     if min_blocks is None and src.launch.grid > TARGET_SMS:
         # enough CTAs per SM for the whole grid to be resident at once, when the registers allow
         per_sm = -(-src.launch.grid // TARGET_SMS)
-        if per_sm * block <= 2048 and 65536 // (per_sm * block) >= 24 + (1 if strict else unroll) * vec:
+        if per_sm * block <= 2048 and 65536 // (per_sm * block) >= 24 + (1 if strict else unroll) * run:
             min_blocks = per_sm
     tree_op = OP_TYPE[comb.tree_op] if comb.tree_op else OP_TYPE[op]
-    em.emit(f"float acc_ = emb::strided_fold<{vec}, {OP_TYPE[op]}, {unroll}, {str(bool(strict)).lower()}>("
-            f"{pointer}, {start}, {step}, {end});")
+    mapped = ""
+    if chain:  # what the body computes from a loaded value before folding it: the statement lowering's expressions
+        keep, em.lines = em.lines, []
+        em.depth += 1
+        em.emit(f"{em.var(load.names[0], 'f32')} = in_;")
+        for a in chain:
+            em.s_Assign(a)
+        code, dt = em.use(value)
+        em.emit(f"return {em.convert(code, dt, 'f32')};")
+        em.depth -= 1
+        inner, em.lines = em.lines, keep
+        em.emit("auto map_ = [&](float in_) -> float {")
+        em.lines += inner
+        em.emit("};")
+        mapped = ", map_"
+    em.emit(f"float acc_ = emb::strided_fold<{run}, {OP_TYPE[op]}, {unroll}, {str(bool(strict)).lower()}>("
+            f"{pointer}, {start}, {step}, {end}{mapped});")
     em.emit(f"acc_ = emb::block_combine<{OP_TYPE[comb.shuffle_op]}, {comb.shuffle_len}, {tree_op}, {comb.tree_len}>"
             f"(acc_, emb_slab);")
     exchange = final_sum(src, op, comb, tail, state)
@@ -280,12 +505,17 @@ def match_reduce(src, strict: bool) -> Plan:
     shared = [f"    __shared__ float emb_slab[{max(comb.tree_len, 1)}];"] + (["    __shared__ float emb_bcast;"] if exchange else [])
     source = finish(em, src, '#include "emb_reduce.cuh"' + ('\n#include "emb_peer.cuh"' if exchange else ""), strict, shared, min_blocks,
                     ["emb::PeerExchange* px"] if exchange else [])
-    how = "in the IR's own order" if strict else f"on {unroll * vec} independent accumulators per thread"
+    how = "in the IR's own order" if strict else f"on {unroll * run} independent accumulators per thread"
     how += f", {unroll} trips in flight per round"
-    remarks = [f"block reduction template: {op} fold of {load.input} in {vec * 4}-byte ld.global.nc runs, {how}",
-               f"butterfly over {comb.shuffle_len} lanes" +
-               (f", then the {comb.tree_len} warps' partials folded in the tree's order by every thread behind one barrier"
-                if comb.tree_len else "")]
+    if regrouped:
+        folds = ", ".join(sorted({f"{c.accum.name} by {c.accum.op.name}" for c in copies}))
+        remarks.append(f"loop {var}: the {block} cooperating threads take contiguous 16-byte chunks (4 t + {4 * block} k + j) instead of "
+                       f"a stride (checked: the partials ({folds}) flow only into combines with the same fold, and no element's "
+                       "value depends on the thread that folds it; the sum is reassociated, so --strict keeps the stride)")
+    remarks += [f"block reduction template: {op} fold of {load.input} in {run * 4}-byte ld.global.nc runs, {how}",
+                f"butterfly over {comb.shuffle_len} lanes" +
+                (f", then the {comb.tree_len} warps' partials folded in the tree's order by every thread behind one barrier"
+                 if comb.tree_len else "")]
     remarks += em.remarks
     if exchange:
         remarks.append("the result is a sum that ends the problem: given an exchange (the element range sharded over GPUs), the "
@@ -419,4 +649,238 @@ def match_softmax(src, strict: bool) -> Plan:
     return Plan("softmax", source, remarks, rows=independent)
 
 
-MATCHERS = (("softmax", match_softmax), ("reduce", match_reduce))
+# ---------------------------------------------------------------- pointwise (elementwise streaming)
+
+POINTWISE_BLOCK = 256   # threads of a CTA of the pointwise template
+POINTWISE_RUN = 4       # consecutive cells a thread owns per run (16 bytes of f32)
+POINTWISE_RUNS = 4      # runs per thread, BLOCK * RUN cells apart, all of their loads in flight before the arithmetic
+STREAM_BYTES = {"f32": 4, "i32": 4, "u32": 4, "f64": 8, "i64": 8, "u64": 8, "f16": 2, "bf16": 2, "i16": 2, "u16": 2,
+                "u8": 1, "i8": 1, "bool": 1, "f8e4m3": 1, "f8e5m2": 1}
+
+
+class PointwiseEmitter(Emitter):
+    """The statement lowering with the streaming accesses of a pointwise body rerouted: a Load or Write that
+    ``stream`` lists (by identity) takes or leaves lane ``j_`` of a register run instead of touching memory."""
+
+    def __init__(self, src, strict: bool):
+        super().__init__(src, plain=False, strict=strict)
+        self.stream: dict = {}  # id(statement) -> (register array, element dtype)
+
+    def s_Load(self, s) -> None:
+        hit = self.stream.get(id(s))
+        if hit is None:
+            return super().s_Load(s)
+        run, dt = hit
+        vdt = self.value_dtype(dt)
+        out = dtype_name(s.dtype) or vdt
+        self.const_from.pop(s.names[0], None)
+        self.reciprocal_of.pop(s.names[0], None)
+        self.emit(f"{self.var(s.names[0], out)} = {self.convert(f'{run}.v[j_]', vdt, out)};")
+
+    def s_Write(self, s) -> None:
+        hit = self.stream.get(id(s))
+        if hit is None:
+            return super().s_Write(s)
+        run, dt = hit
+        code, d = self.use(s.values[0])
+        self.emit(f"{run}.v[j_] = {self.convert(code, d, self.value_dtype(dt))};")
+
+
+def match_pointwise(src, strict: bool) -> Plan:
+    """A Tile whose every thread computes its own cell from Loads, Lets and Assigns and writes it: emmy's
+    pointwise kernels (the statement kinds of emmy_ptx/elementwise.py; one thread per element, scalar accesses).
+    Cells are independent, so which thread owns which cell is free: here a thread owns runs of four cells that are
+    consecutive along the innermost axis and moves each run with one access. The arithmetic stays the statement
+    lowering's, so every mode keeps its results bit for bit (also --strict: no operation is reordered).
+    Conditions: no loop, branch or cross-thread statement; no name read before it is defined (a thread starts a
+    cell with zeros in the IR, here with the previous cell's values) and no use of lane or warp (the template
+    moves the cells between threads); every streamed buffer is indexed [.., innermost axis] with the outer indices
+    free of that axis, row lengths and the axis extent multiples of four, loads from buffers the kernel does not write."""
+    tile = single_tile(src)
+    body = list(tile.body)
+    allowed = ("Load", "Let", "Assign", "Write", "Init", "Select")
+    need(body and all(kind(s) in allowed for s in body), "statements other than Load, Let, Assign, Select, Write")
+    inner = tile.axes[-1]
+    E = inner.extent.as_static()
+    axes = [a.name for a in tile.axes]
+    need(E % POINTWISE_RUN == 0, f"the innermost axis ({E}) is not a multiple of {POINTWISE_RUN}")
+    cells = math.prod(a.extent.as_static() for a in tile.axes)
+
+    defined = set(axes)
+
+    def uses(names):
+        for n in names:
+            need(n not in ("lane", "warp"), "lane or warp is used (the template moves the cells between threads)")
+            need(n in defined, f"{n} is read before it is defined")
+
+    streams = []  # (statement, buffer name, dtype, is_write)
+    for st in body:
+        k = kind(st)
+        if k == "Load":
+            for e in st.index:
+                uses(ir.expr_vars(e))
+            if stream_access(src, st.input, st.index, inner.name) and len(st.names) == 1 and st.input not in src.written:
+                streams.append((st, st.input, src.buffers[st.input].dtype, False))
+            defined.update(st.names)
+        elif k == "Write":
+            for e in st.index:
+                uses(ir.expr_vars(e))
+            uses(st.values)
+            need(not st.atomic, "an atomic Write")
+            need(st.output in src.buffers, "a Write to shared memory")
+            need(stream_access(src, st.output, st.index, inner.name) and len(st.values) == 1,
+                 "a Write that is not one value at [.., innermost axis]")
+            streams.append((st, st.output, src.buffers[st.output].dtype, True))
+        elif k == "Let":
+            uses(ir.expr_vars(st.value))
+            defined.add(st.name)
+        elif k == "Assign":
+            uses(st.args)
+            defined.add(st.name)
+        elif k == "Select":
+            for br in st.branches:
+                uses([br.value])
+                if getattr(br, "select", None) is not None:
+                    uses(ir.expr_vars(br.select))
+            defined.add(st.name)
+        else:  # Init
+            defined.add(st.name)
+    writes = [x for x in streams if x[3]]
+    need(writes, "nothing is written")
+    read_names = {x[1] for x in streams if not x[3]}
+    need(not ({x[1] for x in writes} & read_names), "a buffer is both streamed in and written")
+    need(not any(kind(st) == "Load" and st.input in src.written for st in body), "a Load from a buffer the kernel writes")
+
+    block, run = POINTWISE_BLOCK, POINTWISE_RUN
+    runs = POINTWISE_RUNS if cells >= 2 * TARGET_SMS * block * run * POINTWISE_RUNS else 1
+    per_cta = block * run * runs
+    grid = -(-cells // per_cta)
+    em = PointwiseEmitter(src, strict)
+    em.depth = 1
+    for a in tile.axes:
+        em.var(a.name, "i64")
+        em.facts[a.name] = None
+
+    def decode(cell: str, with_inner: bool) -> None:
+        stride = 1
+        for axis in reversed(tile.axes):
+            n = axis.extent.as_static()
+            if axis is not inner or with_inner:
+                term = cell if stride == 1 else f"({cell} / {stride}LL)"
+                em.emit(f"v_{axis.name} = {term} % {n}LL;")
+            stride *= n
+
+    em.emit(f"const long long first_ = ((long long)blockIdx.x * {runs * block} + threadIdx.x) * {run};")
+    em.emit(f"bool ok_[{runs}];")
+    for i, (st, buf, dt, is_write) in enumerate(streams):
+        em.emit(f"long long at{i}_[{runs}];")
+        if not is_write:
+            em.emit(f"emb::Run4<{CTYPE[dt]}> in{i}_[{runs}];")
+    em.emit("#pragma unroll")
+    em.emit(f"for (int u_ = 0; u_ < {runs}; ++u_) {{")
+    em.depth += 1
+    em.emit(f"long long c_ = first_ + (long long)u_ * {block * run};")
+    em.emit(f"ok_[u_] = c_ < {cells}LL;")
+    em.emit("if (!ok_[u_]) c_ = 0;")
+    decode("c_", True)
+    for i, (st, buf, dt, is_write) in enumerate(streams):
+        index = st.index
+        em.emit(f"at{i}_[u_] = {em.flat(src.buffers[buf].shape, index)};")
+    em.depth -= 1
+    em.emit("}")
+    em.emit("#pragma unroll")
+    em.emit(f"for (int u_ = 0; u_ < {runs}; ++u_) {{")
+    em.depth += 1
+    for i, (st, buf, dt, is_write) in enumerate(streams):
+        if not is_write:
+            em.emit(f"if (ok_[u_]) in{i}_[u_] = emb::load_run(p_{buf} + at{i}_[u_]);")
+    em.depth -= 1
+    em.emit("}")
+    em.emit("#pragma unroll")
+    em.emit(f"for (int u_ = 0; u_ < {runs}; ++u_) {{")
+    em.depth += 1
+    em.emit("if (!ok_[u_]) continue;")
+    em.emit(f"const long long c_ = first_ + (long long)u_ * {block * run};")
+    decode("c_", True)
+    em.emit(f"const long long inner_ = v_{inner.name};")
+    for i, (st, buf, dt, is_write) in enumerate(streams):
+        if is_write:
+            em.emit(f"emb::Run4<{CTYPE[dt]}> out{i}_;")
+            em.stream[id(st)] = (f"out{i}_", dt)
+        else:
+            em.stream[id(st)] = (f"in{i}_[u_]", dt)
+    em.emit("#pragma unroll")
+    em.emit(f"for (int j_ = 0; j_ < {run}; ++j_) {{")
+    em.depth += 1
+    em.emit(f"v_{inner.name} = inner_ + j_;")
+    em.block(body, None)
+    em.depth -= 1
+    em.emit("}")
+    for i, (st, buf, dt, is_write) in enumerate(streams):
+        if is_write:
+            em.emit(f"emb::store_run(p_{buf} + at{i}_[u_], out{i}_);")
+    em.depth -= 1
+    em.emit("}")
+    source = finish(em, src, '#include "emb_pointwise.cuh"', strict, [], None, (), block)
+    ins = [x for x in streams if not x[3]]
+    moved = sum(STREAM_BYTES[dt] for _, _, dt, _ in streams)
+    remarks = [f"pointwise template: {cells} independent cells, {grid} CTAs of {block} threads, {runs} run(s) of {run} consecutive "
+               f"cells per thread; {len(ins)} buffer(s) streamed in with one ld.global.nc.L1::no_allocate per run, {len(writes)} out "
+               f"with one st.global.cs per run ({moved} B per cell), every load of a thread issued before its arithmetic",
+               "the arithmetic is the statement lowering's, statement by statement: the same bits in every mode"]
+    remarks += em.remarks
+    rows = pointwise_rows(src, tile, streams, body, per_cta)
+    return Plan("pointwise", source, remarks, grid=grid, block=block, rows=rows)
+
+
+def stream_access(src, name: str, index, inner: str) -> bool:
+    """Is buffer[index] one element per cell, consecutive in memory for consecutive values of the innermost axis,
+    and 4-element aligned whenever that axis is at a multiple of four?"""
+    buf = src.buffers.get(name)
+    if buf is None or buf.dtype not in STREAM_BYTES or not index or len(index) != len(buf.shape):
+        return False
+    if not is_var(index[-1], inner) or any(inner in ir.expr_vars(e) for e in index[:-1]):
+        return False
+    return len(buf.shape) == 1 or int(buf.shape[-1]) % POINTWISE_RUN == 0
+
+
+def pointwise_rows(src, tile, streams, body, per_cta: int):
+    """Row independence for the host (see Plan.rows): the leading Tile axis is used only as the leading index of
+    full-rank streamed buffers, and a row is a whole number of CTAs."""
+    if len(tile.axes) < 2:
+        return None
+    lead = tile.axes[0].name
+    row_cells = math.prod(a.extent.as_static() for a in tile.axes[1:])
+    if row_cells % per_cta:
+        return None
+    buffers = {}
+    streamed = {id(st) for st, _, _, _ in streams}
+    for st in body:
+        k = kind(st)
+        if id(st) in streamed:
+            buf = src.buffers[st.input if k == "Load" else st.output]
+            if any(lead in ir.expr_vars(e) for e in st.index[1:]):
+                return None
+            if is_var(st.index[0], lead) and int(buf.shape[0]) == tile.axes[0].extent.as_static():
+                buffers[st.input if k == "Load" else st.output] = math.prod(buf.shape[1:]) * STREAM_BYTES[buf.dtype]
+            elif lead in ir.expr_vars(st.index[0]):
+                return None
+            else:
+                buffers[st.input if k == "Load" else st.output] = 0
+        else:
+            used = set()
+            if k == "Load":
+                for e in st.index:
+                    used |= set(ir.expr_vars(e))
+            elif k == "Let":
+                used = set(ir.expr_vars(st.value))
+            elif k == "Assign":
+                used = set(st.args)
+            elif k == "Select":
+                return None
+            if lead in used:
+                return None
+    return dict(count=tile.axes[0].extent.as_static(), ctas_per_row=row_cells // per_cta, buffers=buffers)
+
+
+MATCHERS = (("softmax", match_softmax), ("reduce", match_reduce), ("pointwise", match_pointwise))

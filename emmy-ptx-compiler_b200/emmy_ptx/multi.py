@@ -21,9 +21,95 @@ def shard(units: int, rank: int, world: int) -> range:
     return range(lo, lo + base + (1 if rank < extra else 0))
 
 
-SHARDED_AXIS = {"sum": "elements", "softmax": "rows", "matmul": "rows of A and C (B replicated)",
-                "attention": "(batch, head) pairs", "mlp": "token rows (weights replicated)",
-                "fragments": "rows of A and C (B replicated)"}
+SHARDED_AXIS = {"sum": "element range", "softmax": "rows", "matmul": "rows of A and C (B replicated)",
+                "attention": "(batch, head) pairs", "mlp": "token rows (weights and scales replicated)",
+                "fragments": "rows of A and C (B replicated)", "elementwise": "rows"}
+
+# The full-size workloads: what is sharded, in which units (a unit is the smallest piece a rank may own, so
+# that every shard keeps the alignment its template wants), and which operands are sliced along it.
+#   units(sizes) -> count; build(sizes, count) -> keyword arguments of the problems.* builder for `count` units;
+#   sliced: operand -> how many leading elements one unit is (None: the operand is replicated on every rank)
+FULL_SIZES = {
+    "sum": dict(n=1 << 24), "softmax": dict(rows=8192, cols=4096), "matmul": dict(m=8192, n=8192, k=8192),
+    "attention": dict(batch=8, heads=32, seq=4096, dim=128), "mlp": dict(tokens=16384, d_model=4096, hidden=16384),
+    "fragments": dict(m=8192, n=8192, k=8192), "elementwise": dict(rows=8192, cols=4096),
+}
+SUM_RUN = 1024   # elements per unit of the array sum: one trip of a 256-thread block on 16-byte runs
+ROW_BLOCK = 128  # rows per unit of the tensor-core workloads: one row of output tiles
+
+
+def sum_grid(n: int, block: int = 256, vec: int = 4) -> int:
+    """Blocks of the sum's first kernel: whole waves of 148 SMs, at least two trips per block, at most eight
+    blocks per SM (1184 for 2^24 elements, the geometry the one-GPU measurement was tuned on)."""
+    trips = max(1, n // (block * vec))
+    return 148 * max(1, min(8, trips // (148 * 2))) if trips >= 148 else trips
+
+
+def plan(workload: str, rank: int, world: int, sizes: dict | None = None) -> dict:
+    """How ``rank`` of ``world`` takes part in one workload: ``units`` (what is divided), ``share`` (the
+    contiguous range this rank owns), ``kwargs`` (arguments of the ``problems`` builder for a problem of the
+    share's size), ``slices`` (operand -> (first element, elements) along its leading axis; operands that are
+    not listed are replicated) and ``reshape`` (operand -> the shape the slice takes in the shard's problem).
+    No workload needs data from another rank, except the sum's scalar (``combine_sum`` / ``PeerExchange``)."""
+    z = dict(FULL_SIZES[workload], **(sizes or {}))
+    slices, reshape = {}, {}
+    if workload == "sum":
+        if z["n"] % SUM_RUN:
+            raise ValueError(f"the sum's length {z['n']} is not a multiple of {SUM_RUN}")
+        units = z["n"] // SUM_RUN
+        share = shard(units, rank, world)
+        n = len(share) * SUM_RUN
+        kwargs = dict(n=n, grid=sum_grid(n))
+        slices["x"] = (share.start * SUM_RUN, n)
+    elif workload in ("softmax", "elementwise"):
+        units = z["rows"]
+        share = shard(units, rank, world)
+        kwargs = dict(rows=len(share), cols=z["cols"])
+        slices["x"] = (share.start, len(share))  # (the elementwise workload's bias row is replicated)
+    elif workload in ("matmul", "fragments"):
+        if z["m"] % ROW_BLOCK:
+            raise ValueError(f"M = {z['m']} is not a multiple of {ROW_BLOCK}")
+        units = z["m"] // ROW_BLOCK
+        share = shard(units, rank, world)
+        kwargs = dict(m=len(share) * ROW_BLOCK, n=z["n"], k=z["k"])
+        slices["a" if workload == "matmul" else "x0"] = (share.start * ROW_BLOCK, len(share) * ROW_BLOCK)
+    elif workload == "attention":
+        units = z["batch"] * z["heads"]
+        share = shard(units, rank, world)
+        kwargs = dict(batch=1, heads=len(share), seq=z["seq"], dim=z["dim"])
+        for name in "qkv":
+            slices[name] = (share.start, len(share))
+            reshape[name] = (units, z["seq"], z["dim"])
+    elif workload == "mlp":
+        if z["tokens"] % ROW_BLOCK:
+            raise ValueError(f"{z['tokens']} tokens are not a multiple of {ROW_BLOCK}")
+        units = z["tokens"] // ROW_BLOCK
+        share = shard(units, rank, world)
+        kwargs = dict(tokens=len(share) * ROW_BLOCK, d_model=z["d_model"], hidden=z["hidden"])
+        slices["x"] = (share.start * ROW_BLOCK, len(share) * ROW_BLOCK)
+    else:
+        raise KeyError(workload)
+    if len(share) == 0:
+        raise ValueError(f"{workload}: rank {rank} of {world} gets none of the {units} units")
+    return dict(workload=workload, units=units, share=share, kwargs=kwargs, slices=slices, reshape=reshape,
+                axis=SHARDED_AXIS[workload])
+
+
+def shard_inputs(pl: dict, full: dict, shard_args: list) -> dict:
+    """The shard's host inputs cut out of the full problem's (``full``: name -> numpy array as
+    ``runner.host_inputs`` makes them): sliced operands along their leading axis, everything else whole.
+    ``shard_args`` are the shard problem's meta.json arguments (for the shapes the slices take)."""
+    shapes = {a["name"]: a["shape"] for a in shard_args}
+    out = {}
+    for name, array in full.items():
+        if name in pl["slices"]:
+            lo, count = pl["slices"][name]
+            lead = pl["reshape"].get(name)
+            piece = (array.reshape(lead) if lead else array)[lo:lo + count]
+            out[name] = piece.reshape(shapes[name]).copy()
+        else:
+            out[name] = array
+    return out
 
 
 def combine_sum(partial, strict: bool = False, group=None):

@@ -103,6 +103,40 @@ def array_sum(n: int = 1 << 24, grid: int = 1184, block: int = 256, final_block:
                 tensors={"x": dict(dtype="f32", shape=[n], seed=0, dist="uniform_pm1")})
 
 
+def scalar_fold_body(rows: int, cols: int, block: int, src: str, dst: str, copies: int = 1):
+    """emmy's own spelling of a cooperative sum (examples/r01_array_sum/k_sum_1_reduce.ir.txt:1-12): block r, thread t
+    folds x[r, t], x[r, t + B], ... one scalar at a time; with ``copies`` > 1 the loop is unrolled as emmy does it
+    (step copies * B, copy j reads a + j B into an accumulator of its own, the accumulators merged before the butterfly)."""
+    row = (V("a0"),) if rows > 1 else ()
+    stmts, merges = [], []
+    for j in range(copies):
+        idx = V("a1") if j == 0 else B("+", V("a1"), I(j * block))
+        stmts += [Load(names=(f"in{j}",), input=src, index=(*row, idx), dtype=F32),
+                  Accum(name=f"acc{j}", value=f"in{j}", op="add", dtype=F32, axes=("a1",), base=None)]
+        if j:
+            merges.append(Accum(name="acc0", value=f"acc{j}", op="add", dtype=F32, axes=(), base=None))
+    loop = StridedLoop(axis=Axis(name="a1", extent=cols), start=V("a1_co"), step=I(copies * block), body=tuple(stmts),
+                       unroll=False, end=None, seed=True)
+    tail = Cond(cond=B("==", V("a1_co"), I(0)),
+                body=(Write(output=dst, index=row, values=("acc0",), value_dtype=F32),), else_body=())
+    axes = ((Axis(name="a0", extent=rows),) if rows > 1 else ()) + (Axis(name="a1_co", extent=block),)
+    return (Tile(axes=axes, body=(loop, *merges, *_block_combine("acc0", "add", block), tail), block_threads=block,
+                 aux_threads=0, raster_axes=None, raster_group=None, raster_orient="m"),)
+
+
+def array_sum_scalar(n: int = 1 << 24, grid: int = 1024, block: int = 256, copies: int = 2, ident: str = "r_sum_16m_scalar") -> dict:
+    """The array sum as emmy writes it, before any regrouping: scalar loads strided over the block's threads, x seen as
+    [grid, n / grid] (one row per block), then the same form over the partials."""
+    assert n % grid == 0 and (n // grid) % (copies * block) == 0
+    k1 = dict(node="sum__partial", entry="k_sum__partial", body=scalar_fold_body(grid, n // grid, block, "x", "sum__partial", copies),
+              grid=grid, block=block, inputs=["x"], output=("sum__partial", [grid], "f32"), final=False)
+    k2 = dict(node="sum_1", entry="k_sum_1_reduce", body=scalar_fold_body(1, grid, block, "sum__partial", "sum_1"), grid=1,
+              block=block, inputs=["sum__partial"], output=("sum_1", [], "f32"), final=True)
+    return dict(id=ident, code=f"(torch.rand({n}) * 2 - 1).sum()", rtol=1e-5, atol=1e-5, graph_inputs=["x"],
+                graph_outputs=["sum_1"], kernels=[k1, k2],
+                tensors={"x": dict(dtype="f32", shape=[grid, n // grid], seed=0, dist="uniform_pm1")})
+
+
 # ---------------------------------------------------------------- cfg 2: row softmax
 
 
@@ -330,6 +364,77 @@ def gelu_mlp(tokens: int = 16384, d_model: int = 4096, hidden: int = 16384, lane
                 atol=3e-2, graph_inputs=["x", "w1", "w2"], graph_outputs=["mlp"], kernels=[kern], tensors=tensors)
 
 
+# ---------------------------------------------------------------- pointwise: bias + tanh-GELU, and bias + ReLU + residual
+
+
+def _gelu_tanh(x: str, out: str, tag: str = "") -> list:
+    """out = 0.5 x (1 + tanh(c (x + k x^3))), one Assign per operation (the spelling of tools/corpus_specs.py:104-105
+    after emmy splits it; constants as loaded one-element arguments like examples/k_gelu_mlp/meta.json)."""
+    t = lambda n: f"{n}{tag}"  # noqa: E731
+    return [Assign(name=t("x2"), op="multiply", args=(x, x), dtype=F32),
+            Assign(name=t("x3"), op="multiply", args=(t("x2"), x), dtype=F32),
+            Assign(name=t("u0"), op="multiply", args=(t("x3"), "gk"), dtype=F32),
+            Assign(name=t("u1"), op="add", args=(x, t("u0")), dtype=F32),
+            Assign(name=t("u2"), op="multiply", args=(t("u1"), "gc"), dtype=F32),
+            Assign(name=t("th"), op="tanh", args=(t("u2"),), dtype=F32),
+            Assign(name=t("u3"), op="add", args=("one", t("th")), dtype=F32),
+            Assign(name=t("u4"), op="multiply", args=(x, "half"), dtype=F32),
+            Assign(name=out, op="multiply", args=(t("u3"), t("u4")), dtype=F32)]
+
+
+def bias_gelu_body(rows: int, cols: int, block: int):
+    """One thread per element (emmy's pointwise form): y[r, c] = gelu_tanh(x[r, c] + bias[c])."""
+    consts = (Load(names=("half",), input="gelu_half", index=(I(0),), dtype=F32),
+              Load(names=("gc",), input="gelu_c", index=(I(0),), dtype=F32),
+              Load(names=("gk",), input="gelu_k", index=(I(0),), dtype=F32),
+              Load(names=("one",), input="gelu_one", index=(I(0),), dtype=F32))
+    stmts = (*consts,
+             Load(names=("xv",), input="x", index=(V("a0"), V("a1")), dtype=F32),
+             Load(names=("bv",), input="bias", index=(V("a1"),), dtype=F32),
+             Assign(name="z", op="add", args=("xv", "bv"), dtype=F32),
+             *_gelu_tanh("z", "g"),
+             Write(output="y", index=(V("a0"), V("a1")), values=("g",), value_dtype=F32))
+    return (Tile(axes=(Axis(name="a0", extent=rows), Axis(name="a1", extent=cols)), body=stmts, block_threads=block,
+                 aux_threads=0, raster_axes=None, raster_group=None, raster_orient="m"),)
+
+
+def bias_gelu(rows: int = 8192, cols: int = 4096, block: int = 256, ident: str = "e_bias_gelu_8192x4096"):
+    assert (rows * cols) % block == 0
+    consts = {"gelu_half": 0.5, "gelu_c": GELU_C, "gelu_k": GELU_K, "gelu_one": 1.0}
+    kern = dict(node="y", entry="k_bias_gelu", body=bias_gelu_body(rows, cols, block), grid=rows * cols // block, block=block,
+                inputs=[*consts, "x", "bias"], output=("y", [rows, cols], "f32"), final=True)
+    tensors = {"x": dict(dtype="f32", shape=[rows, cols], seed=0, dist="normal"),
+               "bias": dict(dtype="f32", shape=[cols], seed=1, dist="normal")}
+    for name, value in consts.items():
+        tensors[name] = dict(dtype="f32", shape=[1], data=[value], constant=value)
+    return dict(id=ident, code=f"torch.nn.functional.gelu(torch.randn({rows}, {cols}) + torch.randn({cols}), approximate='tanh')",
+                rtol=1e-5, atol=1e-6, graph_inputs=["x", "bias"], graph_outputs=["y"], kernels=[kern], tensors=tensors)
+
+
+def bias_relu_residual_body(rows: int, cols: int, block: int):
+    """y[r, c] = max(x[r, c] + bias[c], 0) + res[r, c]: three streams of 4 bytes per element, two IEEE additions."""
+    stmts = (Load(names=("xv",), input="x", index=(V("a0"), V("a1")), dtype=F32),
+             Load(names=("bv",), input="bias", index=(V("a1"),), dtype=F32),
+             Load(names=("rv",), input="res", index=(V("a0"), V("a1")), dtype=F32),
+             Assign(name="z", op="add", args=("xv", "bv"), dtype=F32),
+             Assign(name="a", op="relu", args=("z",), dtype=F32),
+             Assign(name="o", op="add", args=("a", "rv"), dtype=F32),
+             Write(output="y", index=(V("a0"), V("a1")), values=("o",), value_dtype=F32))
+    return (Tile(axes=(Axis(name="a0", extent=rows), Axis(name="a1", extent=cols)), body=stmts, block_threads=block,
+                 aux_threads=0, raster_axes=None, raster_group=None, raster_orient="m"),)
+
+
+def bias_relu_residual(rows: int = 8192, cols: int = 4096, block: int = 256, ident: str = "e_bias_relu_res_8192x4096"):
+    assert (rows * cols) % block == 0
+    kern = dict(node="y", entry="k_bias_relu_res", body=bias_relu_residual_body(rows, cols, block), grid=rows * cols // block,
+                block=block, inputs=["x", "bias", "res"], output=("y", [rows, cols], "f32"), final=True)
+    tensors = {"x": dict(dtype="f32", shape=[rows, cols], seed=0, dist="normal"),
+               "bias": dict(dtype="f32", shape=[cols], seed=1, dist="normal"),
+               "res": dict(dtype="f32", shape=[rows, cols], seed=2, dist="normal")}
+    return dict(id=ident, code=f"torch.relu(torch.randn({rows}, {cols}) + torch.randn({cols})) + torch.randn({rows}, {cols})",
+                rtol=0.0, atol=0.0, graph_inputs=["x", "bias", "res"], graph_outputs=["y"], kernels=[kern], tensors=tensors)
+
+
 # ---------------------------------------------------------------- files
 
 
@@ -397,9 +502,10 @@ def matmul_fragments(m: int = 8192, n: int = 8192, k: int = 8192, ident: str = "
 
 
 WORKLOADS = {"sum": array_sum, "softmax": row_softmax, "matmul": matmul_f16, "attention": attention, "mlp": gelu_mlp,
-             "fragments": matmul_fragments}
+             "fragments": matmul_fragments, "elementwise": bias_gelu, "elementwise_add": bias_relu_residual,
+             "sum_scalar": array_sum_scalar}
 
 
 def write_all(root) -> list:
-    """The five full-size workloads, and the matmul once more in fragment form."""
+    """The five full-size workloads, the matmul once more in fragment form, and the two pointwise workloads."""
     return [write(make(), root) for make in WORKLOADS.values()]

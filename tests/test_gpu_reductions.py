@@ -137,3 +137,50 @@ def test_rows_pipeline_gives_the_same_softmax(tmp_path):
     assert same_bits(out.numpy(), whole)
     assert runner.Problem(problems.write(problems.array_sum(n=4096, grid=4, block=128, final_block=64, ident="s"), tmp_path),
                           "optimized").rows_pipeline() is None
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("n,grid,block,copies", [(1 << 18, 512, 128, 2), (1 << 16, 4, 256, 1), (1 << 20, 1024, 256, 4), (4096, 1, 128, 1)])
+def test_array_sum_in_the_scalar_spelling(tmp_path, mode, n, grid, block, copies):
+    """emmy's own form of the cooperative sum (scalar strided loads, unrolled copies): regrouped into 16-byte chunks in
+    the optimizing mode (tolerance of a reassociated sum), the IR's order bit for bit under --strict and --plain."""
+    p = problems.array_sum_scalar(n=n, grid=grid, block=block, copies=copies, ident="t")
+    prob = runner.Problem(problems.write(p, tmp_path), mode)
+    if mode == "optimized" and (n // grid) % (4 * block) == 0:
+        assert "16-byte" in " ".join(prob.kernels[0].ptx.splitlines()[1:2]) or prob.kernels[0].launch_info["family"] == "reduce"
+    got = prob.run()
+    want = oracle_problem(p, prob.host)
+    if mode == "optimized":
+        assert margin(got["sum_1"].reshape(()), want["sum_1"], 1e-5, 1e-5 * np.sqrt(n)) <= 1
+        exact = float(np.sum(prob.host["x"].astype(np.float64)))
+        assert abs(float(got["sum_1"].reshape(-1)[0]) - exact) <= 1e-5 * np.sqrt(n)
+    else:
+        assert same_bits(prob.outputs()["sum__partial"], want["sum__partial"])
+        assert same_bits(got["sum_1"].reshape(()), want["sum_1"])
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_a_regrouped_fold_keeps_its_arithmetic(mode):
+    """Sum of squares times a block-uniform weight, in the scalar spelling: the body's arithmetic travels with the
+    element to its new thread. Integer-valued inputs make every order of additions exact."""
+    from emmy_ptx.ir import Accum, Assign, Axis, BinaryExpr, Cond, Let, Literal, Load, StridedLoop, Tile, Var, Write, datatype
+    f32 = datatype("f32")
+    rows, cols, block = 6, 2048, 128
+    x = np.random.default_rng(5).integers(-8, 9, (rows, cols)).astype(np.float32)
+    w = np.arange(1, rows + 1, dtype=np.float32)
+    loop = StridedLoop(axis=Axis(name="a", extent=cols), start=Var(name="t"), step=Literal(value=block, dtype="int"), body=(
+        Load(names=("v",), input="x", index=(Var(name="r"), Var(name="a")), dtype=None),
+        Assign(name="sq", op="multiply", args=("v", "v"), dtype=f32),
+        Assign(name="ws", op="multiply", args=("sq", "wr"), dtype=f32),
+        Accum(name="s", value="ws", op="add", dtype=f32, axes=(), base=None)), unroll=False, end=None, seed=True)
+    body = (Tile(axes=(Axis(name="r", extent=rows), Axis(name="t", extent=block)), body=(
+        Load(names=("wr",), input="w", index=(Var(name="r"),), dtype=None), loop, *problems._block_combine("s", "add", block),
+        Cond(cond=BinaryExpr(op="==", left=Var(name="t"), right=Literal(value=0, dtype="int")),
+             body=(Write(output="out", index=(Var(name="r"),), values=("s",), value_dtype=f32),), else_body=())),
+        block_threads=block, aux_threads=0, raster_axes=None, raster_group=None, raster_orient="m"),)
+    src = source("k_wsq", body, {"x": x, "w": w}, {"out": np.zeros(rows, np.float32)}, rows, block)
+    got = runner.run_source(src, {"x": x, "w": w, "out": np.zeros(rows, np.float32)}, mode)["out"]
+    assert same_bits(got, ((x.astype(np.float64) ** 2).sum(axis=1) * w).astype(np.float32))
+    if mode == "optimized":
+        from emmy_ptx.lower import Lowerer
+        assert any("contiguous 16-byte chunks" in r for r in Lowerer(src).run().remarks)
