@@ -13,6 +13,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <cstdio>
 
 #define EMB_STRICT 1
@@ -31,7 +32,8 @@ constexpr int MAX_DEVICES = 64;
 // for the symbol, not a device address: the address comes from cudaGetSymbolAddress, per device.
 static __device__ __align__(256) float g_partials[EMB_STATIC_SUM_MAX_BLOCKS];
 
-float* g_partials_address[MAX_DEVICES] = {};
+// (looked up once per device; host threads may race to do so, and all of them store the same address)
+std::atomic<float*> g_partials_address[MAX_DEVICES] = {};
 
 __global__ void __launch_bounds__(THREADS) sum_partials_static(const float* __restrict__ x, long long n, float* __restrict__ partials) {
     __shared__ float slab[THREADS / 32];
@@ -71,14 +73,13 @@ extern "C" int emb_array_sum_f32_static(const float* x, uint64_t n, uint32_t blo
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     if (device < 0 || device >= MAX_DEVICES) return emb_fail_text(EMB_E_ARGUMENT, "array_sum_static: device index out of range");
-    if (!g_partials_address[device]) {
+    float* partials = g_partials_address[device].load(std::memory_order_relaxed);
+    if (!partials) {
         // set-up, once per device, with that device current: the symbol's address on THIS device
-        float* p = nullptr;
-        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_partials);
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&partials), g_partials);
         if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_partials)");
-        g_partials_address[device] = p;
+        g_partials_address[device].store(partials, std::memory_order_relaxed);
     }
-    float* partials = g_partials_address[device];
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     sum_partials_static<<<blocks, THREADS, 0, s>>>(x, static_cast<long long>(n), partials);
     e = cudaGetLastError();

@@ -123,74 +123,127 @@ def inner_trips(stmts) -> int:
     return total
 
 
+class Placement:
+    """Where the Tile's coordinates fall on the launch. Cells are numbered row-major over the axes and dealt to
+    threads in order, ``block`` per CTA, so an axis whose period (its stride times its extent) divides the block
+    varies only with the thread inside a CTA, and an axis whose stride is a multiple of the block varies only with
+    the CTA; anything else straddles CTA boundaries."""
+
+    def __init__(self, tile, block: int):
+        self.block = block
+        self.extent = {a.name: a.extent.as_static() for a in tile.axes}
+        names = [a.name for a in tile.axes]
+        self.stride = {name: math.prod(self.extent[m] for m in names[i + 1:]) for i, name in enumerate(names)}
+        self.cells = math.prod(self.extent.values())
+
+    def within_cta(self, name: str) -> bool:
+        period = self.stride[name] * self.extent[name]
+        return self.stride[name] < self.block and self.block % period == 0
+
+    def across_ctas(self, name: str) -> bool:
+        return self.stride[name] >= self.block and self.stride[name] % self.block == 0
+
+    def straddlers(self) -> list:
+        return [n for n in self.extent if not (self.within_cta(n) or self.across_ctas(n))]
+
+    def thread_extents(self) -> dict:
+        """coordinate -> extent, for the coordinates that enumerate threads of one CTA"""
+        return {n: self.extent[n] for n in self.extent if self.within_cta(n)}
+
+    def neighbour_axis(self):
+        """The coordinate that steps from one CTA to the next (stride exactly one block) if a cluster's worth of its
+        values is a whole number of clusters, else None: the CTAs of a cluster then differ in it alone."""
+        for n in self.extent:
+            if self.stride[n] == self.block and self.extent[n] % CLUSTER == 0:
+                return n
+        return None
+
+
 def plan(tile, grid: int, block: int):
     """A ClusterPlan, or the reason (a string) why the Tile's work is not shared across a cluster."""
-    extents = [a.extent.as_static() for a in tile.axes]
-    n = math.prod(extents)
-    if tile.aux_threads or (tile.raster_axes and tile.raster_group is not None) or n != grid * block:
+    where = Placement(tile, block)
+    rasterized = bool(tile.raster_axes) and tile.raster_group is not None
+    if tile.aux_threads or rasterized or where.cells != grid * block:
         return "rasterized, banded, or threads outside the Tile"
     if grid % CLUSTER:
         return f"the grid is not a multiple of {CLUSTER}"
-    stride, column, threads = n, None, {}
-    for axis, extent in zip(tile.axes, extents):
-        stride //= extent
-        if stride < block:
-            if block % (stride * extent):
-                return "a coordinate straddles block boundaries"
-            threads[axis.name] = extent
-        elif stride % block:
-            return "a coordinate straddles block boundaries"
-        elif stride == block and extent % CLUSTER == 0:
-            column = axis.name
+    if where.straddlers():
+        return "a coordinate straddles block boundaries"
+    column = where.neighbour_axis()
     if column is None:
         return "no coordinate steps from one block to the next with an extent that is a multiple of 8"
-    body = list(tile.body)
+    body = tuple(tile.body)
     reason = "no loop with work to share"
-    for i, s in enumerate(body):
-        if kind(s) not in ("Loop", "StridedLoop"):
+    for at, stmt in enumerate(body):
+        if kind(stmt) not in ("Loop", "StridedLoop"):
             continue
-        found = split(s, column, threads)
-        if isinstance(found, str):
-            reason = found
-            continue
-        shared, own, values, trips, start, step = found
-        return ClusterPlan(tuple(body[:i]), s, shared, own, tuple(body[i + 1:]), values, trips, trips // CLUSTER, start, step)
+        cut = LoopCut(stmt, column, where.thread_extents())
+        refusal = cut.refusal()
+        if refusal is None:
+            return ClusterPlan(body[:at], stmt, cut.shared, cut.own, body[at + 1:], cut.values, cut.trips, cut.trips // CLUSTER,
+                               cut.start, cut.step)
+        reason = refusal
     return reason
 
 
-def split(loop, column: str, threads: dict):
-    if loop.unroll or any(kind(t) not in PURE for t in ir.walk(loop.body)):
-        return "the loop is not pure"
-    extent = loop.axis.extent.as_static()
-    if kind(loop) == "Loop":
-        start, step, trips = ir.Literal(value=0, dtype="int"), 1, extent
-    else:
-        if loop.end is not None or kind(loop.step) != "Literal":
-            return "the loop's bounds differ between threads"
-        step = int(loop.step.value)
-        start = loop.start
-        if kind(start) != "Var" or threads.get(start.name) != step or extent % step:
-            return "the loop does not start at a thread coordinate equal to its step"
-        trips = extent // step
-    if trips % CLUSTER:
-        return f"the trip count is not a multiple of {CLUSTER}"
-    dep = dependents(loop.body, {column})
-    own = tuple(s for s in loop.body if writes(s) & dep)
-    shared = tuple(s for s in loop.body if s not in own)
-    if not own or not shared:
-        return "nothing to share, or nothing that depends on the column"
-    if any(kind(s) == "Accum" for s in shared):
-        return "the shared part carries a fold across iterations"
-    made = set().union(*(writes(s) for s in shared))
-    needed = set().union(*(all_reads(s) for s in own))
-    values = tuple(sorted(made & needed))
-    if not values or len(values) > MAX_VALUES:
-        return f"{len(values)} values would pass from the shared part to the column's part (1..{MAX_VALUES} allowed)"
-    for v in values:
-        defs = [t for t in ir.walk(shared) if kind(t) in ("Assign", "Accum") and t.name == v]
-        if not defs or any(ir.dtype_name(t.dtype) not in (None, "f32") for t in defs):
-            return f"{v} is not an f32 value the shared part computes"
-    work = trips * max(1, inner_trips(shared))
-    if work < MIN_SHARED_WORK:
-        return f"only {work} shared inner iterations (fewer than {MIN_SHARED_WORK})"
-    return shared, own, values, trips, start, step
+class LoopCut:
+    """One loop of the Tile cut into the part every CTA of a cluster computes alike (it never reads the column) and the
+    part that is the CTA's own; ``refusal()`` runs the legality checks in order and leaves the cut in the attributes."""
+
+    def __init__(self, loop, column: str, thread_extents: dict):
+        self.loop, self.column, self.thread_extents = loop, column, thread_extents
+        self.start, self.step, self.trips = ir.Literal(value=0, dtype="int"), 1, 0
+        self.shared = self.own = self.values = ()
+
+    def refusal(self):
+        for check in (self.purity, self.iteration_space, self.partition, self.handover, self.worth):
+            why = check()
+            if why is not None:
+                return why
+        return None
+
+    def purity(self):
+        impure = any(kind(t) not in PURE for t in ir.walk(self.loop.body))
+        return "the loop is not pure" if impure or self.loop.unroll else None
+
+    def iteration_space(self):
+        """Every thread must make the same trips, numbered alike in all CTAs of the cluster: a counted Loop, or a
+        StridedLoop whose start is a thread coordinate that runs over exactly one step."""
+        loop, extent = self.loop, self.loop.axis.extent.as_static()
+        if kind(loop) == "Loop":
+            self.trips = extent
+        else:
+            if loop.end is not None or kind(loop.step) != "Literal":
+                return "the loop's bounds differ between threads"
+            self.step, self.start = int(loop.step.value), loop.start
+            lanes = self.thread_extents.get(self.start.name) if kind(self.start) == "Var" else None
+            if lanes != self.step or extent % self.step:
+                return "the loop does not start at a thread coordinate equal to its step"
+            self.trips = extent // self.step
+        return None if self.trips % CLUSTER == 0 else f"the trip count is not a multiple of {CLUSTER}"
+
+    def partition(self):
+        tainted = dependents(self.loop.body, {self.column})
+        self.own = tuple(s for s in self.loop.body if writes(s) & tainted)
+        self.shared = tuple(s for s in self.loop.body if not (writes(s) & tainted))
+        if not (self.own and self.shared):
+            return "nothing to share, or nothing that depends on the column"
+        if any(kind(s) == "Accum" for s in self.shared):
+            return "the shared part carries a fold across iterations"
+        return None
+
+    def handover(self):
+        produced = {name for s in self.shared for name in writes(s)}
+        consumed = {name for s in self.own for name in all_reads(s)}
+        self.values = tuple(sorted(produced & consumed))
+        if not 1 <= len(self.values) <= MAX_VALUES:
+            return f"{len(self.values)} values would pass from the shared part to the column's part (1..{MAX_VALUES} allowed)"
+        for v in self.values:
+            makers = [t for t in ir.walk(self.shared) if kind(t) in ("Assign", "Accum") and t.name == v]
+            if not makers or any(ir.dtype_name(t.dtype) not in (None, "f32") for t in makers):
+                return f"{v} is not an f32 value the shared part computes"
+        return None
+
+    def worth(self):
+        work = self.trips * max(1, inner_trips(self.shared))
+        return None if work >= MIN_SHARED_WORK else f"only {work} shared inner iterations (fewer than {MIN_SHARED_WORK})"

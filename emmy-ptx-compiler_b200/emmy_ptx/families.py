@@ -447,6 +447,8 @@ def match_reduce(src, strict: bool, disable=frozenset()) -> Plan:
         need(row % 4 == 0, "the row length is not a multiple of the 16-byte run")
         run, start, step, end = 4, f"(long long)v_{t_axis} * 4LL", f"{B4}LL", f"{extent}LL"
         trips = extent // B4
+        if trips > 8 and REDUCE_UNROLL is None:  # two rounds of eight 16-byte loads in flight rather than sixteen at once
+            trips = None
     else:
         run = vec
         em.facts[var] = (loop.start, loop.step)

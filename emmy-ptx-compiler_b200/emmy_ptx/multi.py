@@ -23,7 +23,8 @@ def shard(units: int, rank: int, world: int) -> range:
 
 SHARDED_AXIS = {"sum": "element range", "softmax": "rows", "matmul": "rows of A and C (B replicated)",
                 "attention": "(batch, head) pairs", "mlp": "token rows (weights and scales replicated)",
-                "fragments": "rows of A and C (B replicated)", "elementwise": "rows"}
+                "fragments": "rows of A and C (B replicated)", "elementwise": "rows (the bias row replicated)",
+                "elementwise_add": "rows (the bias row replicated)"}
 
 # The full-size workloads: what is sharded, in which units (a unit is the smallest piece a rank may own, so
 # that every shard keeps the alignment its template wants), and which operands are sliced along it.
@@ -33,6 +34,7 @@ FULL_SIZES = {
     "sum": dict(n=1 << 24), "softmax": dict(rows=8192, cols=4096), "matmul": dict(m=8192, n=8192, k=8192),
     "attention": dict(batch=8, heads=32, seq=4096, dim=128), "mlp": dict(tokens=16384, d_model=4096, hidden=16384),
     "fragments": dict(m=8192, n=8192, k=8192), "elementwise": dict(rows=8192, cols=4096),
+    "elementwise_add": dict(rows=8192, cols=4096),
 }
 SUM_RUN = 1024   # elements per unit of the array sum: one trip of a 256-thread block on 16-byte runs
 ROW_BLOCK = 128  # rows per unit of the tensor-core workloads: one row of output tiles
@@ -61,11 +63,12 @@ def plan(workload: str, rank: int, world: int, sizes: dict | None = None) -> dic
         n = len(share) * SUM_RUN
         kwargs = dict(n=n, grid=sum_grid(n))
         slices["x"] = (share.start * SUM_RUN, n)
-    elif workload in ("softmax", "elementwise"):
+    elif workload in ("softmax", "elementwise", "elementwise_add"):
         units = z["rows"]
         share = shard(units, rank, world)
         kwargs = dict(rows=len(share), cols=z["cols"])
-        slices["x"] = (share.start, len(share))  # (the elementwise workload's bias row is replicated)
+        for name in ("x", "res") if workload == "elementwise_add" else ("x",):
+            slices[name] = (share.start, len(share))  # (the pointwise workloads' bias row is replicated)
     elif workload in ("matmul", "fragments"):
         if z["m"] % ROW_BLOCK:
             raise ValueError(f"M = {z['m']} is not a multiple of {ROW_BLOCK}")

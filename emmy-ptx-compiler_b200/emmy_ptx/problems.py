@@ -134,7 +134,7 @@ def array_sum_scalar(n: int = 1 << 24, grid: int = 1024, block: int = 256, copie
               block=block, inputs=["sum__partial"], output=("sum_1", [], "f32"), final=True)
     return dict(id=ident, code=f"(torch.rand({n}) * 2 - 1).sum()", rtol=1e-5, atol=1e-5, graph_inputs=["x"],
                 graph_outputs=["sum_1"], kernels=[k1, k2],
-                tensors={"x": dict(dtype="f32", shape=[grid, n // grid], seed=0, dist="uniform_pm1")})
+                tensors={"x": dict(dtype="f32", shape=[grid, n // grid] if grid > 1 else [n], seed=0, dist="uniform_pm1")})
 
 
 # ---------------------------------------------------------------- cfg 2: row softmax

@@ -165,6 +165,18 @@ class CompiledKernel:
         return out
 
 
+WAIT_CODES = {1: "shared-memory stage never filled", 2: "shared-memory stage never released",
+              3: "accumulator never completed", 4: "accumulator never drained"}  # emb::tc::WAIT_* of csrc/templates/emb_tc.cuh
+
+
+def raise_on_status(entry: str, word: list) -> None:
+    """The status word a tensor-core template's bounded waits report into: [0] the first failure's code (0: none),
+    [1] the CTA, [2] the step it was waiting at. A non-zero code becomes ``EmbError(-3)``."""
+    if word and word[0]:
+        where = WAIT_CODES.get(word[0], "wait")
+        raise driver.EmbError(-3, f"{entry}: a bounded wait ran out ({where}; code {word[0]}, CTA {word[1]}, step {word[2]})")
+
+
 EXCHANGE = "__exchange__"  # key of the exchange record among a problem's tensors (shared by all buffer sets)
 
 
@@ -264,12 +276,7 @@ class Problem:
         for tensors in [self.tensors] + list(getattr(self, "copies", [])):
             for name, t in tensors.items():
                 if name.endswith(".status") and t.dtype == torch.int32:
-                    word = t.cpu().tolist()
-                    if word[0]:
-                        where = {1: "shared-memory stage never filled", 2: "shared-memory stage never released",
-                                 3: "accumulator never completed", 4: "accumulator never drained"}.get(word[0], "wait")
-                        raise driver.EmbError(-3, f"{name[:-7]}: a bounded wait ran out ({where}; code {word[0]}, "
-                                                  f"CTA {word[1]}, step {word[2]})")
+                    raise_on_status(name[:-7], t.cpu().tolist())
 
     def outputs(self) -> dict:
         names = [a["name"] for k in self.meta["kernels"] for a in k["args"] if a.get("output")]
@@ -283,6 +290,8 @@ class Problem:
     def rotate(self, min_bytes: int = 512 << 20, max_sets: int = 16) -> int:
         """Bind further copies of every tensor until the sets together hold ``min_bytes``:
         timing then walks the sets, so a run never finds its data in the 126 MB L2."""
+        if getattr(self, "guards", None):
+            raise driver.EmbError(-2, "rotate() on a canary problem: the copies would have no guard zones (check one set, time another problem)")
         per_set = sum(t.numel() * t.element_size() for n, t in self.tensors.items() if n != EXCHANGE)
         want = max(2, min(max_sets, -(-min_bytes // max(per_set, 1))))
         self.copies = getattr(self, "copies", [])
@@ -299,9 +308,9 @@ class Problem:
         return out
 
     def rows_pipeline(self, chunks: int = 4, streams: int = 3):
-        """For a one-kernel problem whose launch header declares its rows independent (one CTA per row of the listed
-        buffers): a callable ``run(host_in, host_out)`` that processes the rows in ``chunks`` slices, each slice's
-        host-to-device copy, launch and device-to-host copy on one of ``streams`` CUDA streams, so that the copies of
+        """For a one-kernel problem whose launch header declares its rows independent (a fixed number of CTAs per row of
+        the listed buffers, one unless the header says otherwise): a callable ``run(host_in, host_out)`` that processes
+        the rows in ``chunks`` slices, each slice's host-to-device copy, launch and device-to-host copy on one of ``streams`` CUDA streams, so that the copies of
         one slice overlap the compute and the opposite-direction copies of its neighbours. ``host_in`` / ``host_out``
         map buffer names to pinned host tensors of the full shapes. Returns None when the kernel declares no such rows."""
         import torch
@@ -311,7 +320,7 @@ class Problem:
         info = k.launch_info.get("rows")
         if not info or any(p["kind"] != "buffer" for p in k.launch_info["params"]):
             return None
-        total = info["count"]
+        total, per_row = info["count"], info.get("ctas_per_row", 1)
         bounds = [total * c // chunks for c in range(chunks + 1)]
         pool = [torch.cuda.Stream(self.device) for _ in range(streams)]
         li = k.launch_info
@@ -321,10 +330,11 @@ class Problem:
             if hi == lo:
                 continue
             params = [self.tensors[p["name"]].data_ptr() + lo * info["buffers"].get(p["name"], 0) for p in li["params"]]
-            pieces.append((lo, hi, driver.Launch(k.function, [hi - lo, 1, 1], li["block"], li.get("cluster", 1),
+            pieces.append((lo, hi, driver.Launch(k.function, [(hi - lo) * per_row, 1, 1], li["block"], li.get("cluster", 1),
                                                  li.get("smem_bytes", 0), params)))
-        ins = [n for n in info["buffers"] if n in self.host]
-        outs = [n for n in info["buffers"] if n not in self.host]
+        # buffers every row shares (0 bytes per row: a bias row, a scalar) stay where they are
+        ins = [n for n, row_bytes in info["buffers"].items() if n in self.host and row_bytes]
+        outs = [n for n, row_bytes in info["buffers"].items() if n not in self.host and row_bytes]
 
         def run(host_in: dict, host_out: dict) -> None:
             main = torch.cuda.current_stream(self.device)
@@ -335,7 +345,8 @@ class Problem:
                 s.wait_event(start)
                 with torch.cuda.stream(s):
                     for n in ins:
-                        self.tensors[n][lo:hi].copy_(host_in[n][lo:hi], non_blocking=True)
+                        if n in host_in:
+                            self.tensors[n][lo:hi].copy_(host_in[n][lo:hi], non_blocking=True)
                     driver.launch([launch], s.cuda_stream)
                     for n in outs:
                         host_out[n][lo:hi].copy_(self.tensors[n][lo:hi], non_blocking=True)

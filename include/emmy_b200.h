@@ -20,7 +20,10 @@
  * the library owns the modules it loaded until emb_module_unload. The library
  * uses the device's primary context, the one the CUDA runtime and torch use,
  * so pointers and streams are interchangeable. Calls are thread-safe as far
- * as the driver's are; there is no global state beyond the context.
+ * as the driver's are; there is no global state beyond the context, with one
+ * exception: emb_array_sum_f32_static keeps a device array per GPU and a
+ * process-wide table of its addresses, and, being written against the CUDA
+ * runtime, returns cudaError_t values (> 0) where the others return CUresult.
  */
 #ifndef EMMY_B200_H
 #define EMMY_B200_H

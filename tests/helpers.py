@@ -41,6 +41,23 @@ def margin(got, want, rtol: float, atol: float) -> float:
     return float(np.max(np.abs(got - want) / (atol + rtol * np.abs(want)))) if got.size else 0.0
 
 
+def stated_margin(got, want, rtol: float, name: str | None = None) -> float:
+    """The margin at a STATED tolerance, exactly as the reference's runner judges a problem
+    (tools/run_suite.py:97-104: max |got - want| / (atol + rtol |want|)) with atol = rtol * RMS(want) over the whole
+    compared set: nothing added for the output format's last place, no per-row scale. With ``name`` and the
+    environment variable EMB_MARGIN_REPORT set, the value is appended to that file (one JSON object per line), which
+    is how the table of measured margins is made."""
+    import json
+    import os
+    want64 = np.asarray(want, np.float64)
+    value = margin(got, want64, rtol, rtol * float(np.sqrt(np.mean(want64 ** 2))) if want64.size else 0.0)
+    report = os.environ.get("EMB_MARGIN_REPORT")
+    if name and report:
+        with open(report, "a") as f:
+            f.write(json.dumps(dict(case=name, rtol=rtol, margin=value, cells=int(want64.size))) + "\n")
+    return value
+
+
 def oracle_problem(problem: dict, host: dict, blocks=None) -> dict:
     """Run every kernel of an authored problem (emmy_ptx.problems) through the oracle."""
     from emmy_ptx import runner

@@ -74,3 +74,18 @@ int main() {
     subprocess.run(["nvcc", "-x", "cu", "-I", str(ROOT / "include"), "-I", str(templates), "-o", str(exe), str(src)], check=True)
     out = subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()
     assert [int(v) for v in out] == [multi.RECORD_BYTES, 64, 72, 76, 80, multi.RECORD_BYTES]
+
+
+def test_a_status_word_becomes_an_error_with_code_cta_and_step():
+    """What the host makes of a template's bounded wait that gave up (no GPU needed: the word is synthetic)."""
+    import pytest
+
+    from emmy_ptx import driver, runner
+    runner.raise_on_status("k_matmul", [0, 7, 9, 0, 0, 0, 0, 0])  # nothing happened
+    with pytest.raises(driver.EmbError) as err:
+        runner.raise_on_status("k_matmul", [3, 41, 1005, 0, 0, 0, 0, 0])
+    assert err.value.code == -3
+    text = str(err.value)
+    assert "k_matmul" in text and "accumulator never completed" in text and "code 3, CTA 41, step 1005" in text
+    with pytest.raises(driver.EmbError, match="code 5, CTA 2, step 100"):
+        runner.raise_on_status("k_attention", [5, 2, 100])

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 from emmy_ptx import problems, runner
-from helpers import oracle_problem
+from helpers import oracle_problem, stated_margin
 
 pytestmark = pytest.mark.gpu
 RTOL = 2e-3
@@ -16,12 +16,17 @@ RTOL = 2e-3
 ULP = {"f16": 2.0 ** -10, "bf16": 2.0 ** -7}
 
 
-def check(got, want, dtype="f16"):
-    """The stated 2e-3 plus the format's allowance above; near zero the scale is the RMS of the output
-    ROW (an output row is a weighted mean of V rows: its small entries carry the rounding of its large ones,
-    and early causal rows are an order of magnitude larger than late ones)."""
+def check(got, want, dtype="f16", name=None):
+    """f16 results are held to the STATED tolerance as it stands (rtol = 2e-3, atol = rtol * RMS of the compared set,
+    nothing added); additionally, and for bf16 instead, to the stated 2e-3 plus the format's allowance above with the
+    RMS of the output ROW as the scale near zero (an output row is a weighted mean of V rows: its small entries
+    carry the rounding of its large ones, and early causal rows are an order of magnitude larger than late ones,
+    so the per-row scale is the STRICTER one for late rows). The bf16 margin at the stated 2e-3 is recorded."""
     want64 = np.asarray(want, np.float64)
     got64 = np.asarray(got, np.float64)
+    stated = stated_margin(got64, want64, RTOL, name and f"attention {dtype} {name}")
+    if dtype == "f16":
+        assert stated <= 1, stated
     rtol = RTOL + ULP[dtype]
     atol = rtol * np.sqrt(np.mean(want64 ** 2, axis=-1, keepdims=True))
     assert float(np.max(np.abs(got64 - want64) / (atol + rtol * np.abs(want64)))) <= 1
@@ -37,7 +42,7 @@ def sampled(batch_heads: int, seq: int):
 def compare_rows(p, prob, got, dtype="f16", host=None):
     blocks = sampled(got.shape[0] * got.shape[1], got.shape[2])
     want = oracle_problem(p, host or prob.host, blocks=blocks)["attn"].reshape(-1, 128)
-    check(got.reshape(-1, 128)[blocks], want[blocks], dtype)
+    check(got.reshape(-1, 128)[blocks], want[blocks], dtype, f"{got.shape} sampled rows vs oracle")
 
 
 @pytest.mark.parametrize("batch,heads,seq,causal,dtype", [(1, 2, 256, True, "f16"), (1, 1, 128, True, "f16"),
@@ -55,7 +60,7 @@ def test_attention_small_against_the_oracle(tmp_path, batch, heads, seq, causal,
     if causal:
         s = np.where(np.tril(np.ones((seq, seq), bool)), s, -np.inf)
     w = np.exp(s - s.max(axis=-1, keepdims=True))
-    check(got, np.einsum("bhqk,bhkd->bhqd", w / w.sum(axis=-1, keepdims=True), v), dtype)
+    check(got, np.einsum("bhqk,bhkd->bhqd", w / w.sum(axis=-1, keepdims=True), v), dtype, f"{got.shape} causal={causal} all rows vs f64")
 
 
 def test_attention_strict_keeps_the_ir_order(tmp_path):
@@ -89,12 +94,12 @@ def test_attention_full_size_sampled_rows_and_cross_check():
     rows = [0, 1, 127, 128, 255, 256, 300]
     blocks = sorted({bh * 4096 + r for bh in (0, 77, 255) for r in rows})  # one block per (batch, head, query)
     want = oracle_problem(p, prob.host, blocks=blocks)["attn"].reshape(-1, 128)
-    check(got.reshape(-1, 128)[blocks], want[blocks])
+    check(got.reshape(-1, 128)[blocks], want[blocks], "f16", "8x32x4096x128 sampled rows vs oracle")
     # every row of the first and last batch against an f32 attention on the same device (a cross-check,
     # not the oracle)
     for b in (0, 7):
         q, k, v = (prob.tensors[n][b:b + 1].float() for n in "qkv")
         ref = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True).cpu().numpy()
-        check(got[b:b + 1], ref)
+        check(got[b:b + 1], ref, "f16", f"8x32x4096x128 batch {b} vs f32 attention")
     # the first query of every (batch, head) attends to key 0 only: its output is V[.., 0, :] exactly
     assert np.array_equal(got[:, :, 0, :], prob.host["v"][:, :, 0, :])

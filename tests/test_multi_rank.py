@@ -122,3 +122,114 @@ def test_exchange_protocol_with_ranks_as_threads():
     want = [float(np.float32(sum(range(1, world + 1))) * np.float32(q)) for q in range(1, steps + 1)]
     for r in range(world):
         assert results[r] == want
+
+
+# ---------------------------------------------------------------- sharding plans: N ranks solve the one-GPU problem
+
+SMALL = {"sum": dict(n=1 << 14), "softmax": dict(rows=24, cols=256), "matmul": dict(m=384, n=64, k=64),
+         "attention": dict(batch=2, heads=3, seq=32, dim=16), "mlp": dict(tokens=384, d_model=64, hidden=64),
+         "fragments": dict(m=384, n=64, k=64), "elementwise": dict(rows=24, cols=256), "elementwise_add": dict(rows=24, cols=256)}
+
+
+def _full_inputs(workload, sizes):
+    from emmy_ptx import problems, runner
+    full = problems.WORKLOADS[workload](ident="full", **multi.plan(workload, 0, 1, sizes)["kwargs"])
+    meta = problems._meta(full)
+    host = {}
+    for km in meta["kernels"]:
+        host.update(runner.host_inputs(km["args"]))
+    return full, host
+
+
+@pytest.mark.parametrize("workload", sorted(SMALL))
+def test_plans_partition_every_workload(workload):
+    """Every unit belongs to one rank; the sliced operands of all ranks put together are the full operands, everything
+    else is replicated; the shard problems have the shapes their slices need."""
+    from emmy_ptx import problems
+    sizes = SMALL[workload]
+    _, host = _full_inputs(workload, sizes)
+    for world in (1, 2, 3):
+        plans = [multi.plan(workload, r, world, sizes) for r in range(world)]
+        assert sum(len(p["share"]) for p in plans) == plans[0]["units"]
+        assert all(a["share"].stop == b["share"].start for a, b in zip(plans, plans[1:]))
+        pieces = {}
+        for r, pl in enumerate(plans):
+            shard = problems.WORKLOADS[workload](ident=f"s{r}", **pl["kwargs"])
+            args = [a for km in problems._meta(shard)["kernels"] for a in km["args"]]
+            ins = multi.shard_inputs(pl, host, args)
+            shapes = {a["name"]: tuple(a["shape"]) for a in args if not a.get("output") and not a.get("intermediate")}
+            for name, array in ins.items():
+                assert tuple(array.shape) == shapes[name], (name, array.shape, shapes[name])
+                if name in pl["slices"]:
+                    pieces.setdefault(name, []).append(array.reshape(-1))
+                else:
+                    assert array is host[name]
+        for name, parts in pieces.items():
+            assert np.array_equal(np.concatenate(parts).view(np.uint8), host[name].reshape(-1).view(np.uint8)), name
+    with pytest.raises(ValueError):
+        multi.plan(workload, 10 ** 6 - 1, 10 ** 6, sizes)  # more ranks than units: the last ranks would get nothing
+
+
+def test_the_sums_grid_keeps_whole_waves():
+    assert multi.sum_grid(1 << 24) == 1184 and multi.sum_grid(1 << 21) == 888 and multi.sum_grid(1 << 14) == 16
+    for world in (2, 4, 8):
+        pl = multi.plan("sum", world - 1, world)
+        assert pl["kwargs"]["n"] * world == 1 << 24 and pl["kwargs"]["grid"] % 148 == 0
+
+
+def _sharded_rank(rank, world, port, workload, out):
+    """One rank of a CPU run: its shard of the workload through the oracle (standing in for the GPU kernels), the sum's
+    scalars combined as the bench does without peer memory."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from emmy_ptx import problems, runner
+    from oracle import ir_oracle
+    sizes = SMALL[workload]
+    _, host = _full_inputs(workload, sizes)
+    pl = multi.plan(workload, rank, world, sizes)
+    shard = problems.WORKLOADS[workload](ident="s", **pl["kwargs"])
+    args = [a for km in problems._meta(shard)["kernels"] for a in km["args"]]
+    bufs = dict(multi.shard_inputs(pl, host, args))
+    for kern in shard["kernels"]:
+        name, shape, dt = kern["output"]
+        bufs[name] = np.zeros(shape, runner.numpy_dtype(dt))
+        ir_oracle.run(kern["body"], bufs, kern["grid"], kern["block"])
+    final = shard["kernels"][-1]["output"][0]
+    result = np.asarray(bufs[final], np.float32).reshape(-1)
+    if workload == "sum":
+        result = multi.combine_sum(torch.from_numpy(result.copy()), strict=True).numpy()
+    out.put((rank, result))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("workload", ["sum", "softmax", "attention", "elementwise_add"])
+def test_two_ranks_solve_the_one_rank_problem(workload):
+    """Strong scaling on the host: two gloo ranks each run their shard; put together (rows, pairs) or combined in rank
+    order (the sum) the results are the one-rank problem's - bit for bit where rows are independent."""
+    from emmy_ptx import problems, runner
+    from oracle import ir_oracle
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_sharded_rank, args=(r, 2, port, workload, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(out.get(timeout=180) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    full, host = _full_inputs(workload, SMALL[workload])
+    bufs = dict(host)
+    for kern in full["kernels"]:
+        name, shape, dt = kern["output"]
+        bufs[name] = np.zeros(shape, runner.numpy_dtype(dt))
+        ir_oracle.run(kern["body"], bufs, kern["grid"], kern["block"])
+    want = np.asarray(bufs[full["kernels"][-1]["output"][0]], np.float32).reshape(-1)
+    if workload == "sum":
+        assert np.array_equal(results[0], results[1])  # every rank holds the same bits
+        assert abs(float(results[0][0]) - float(want[0])) <= 1e-5 * np.sqrt(SMALL["sum"]["n"])
+    else:
+        assert np.array_equal(np.concatenate([results[0], results[1]]).view(np.uint32), want.view(np.uint32))
