@@ -124,7 +124,7 @@ def scalar_fold_body(rows: int, cols: int, block: int, src: str, dst: str, copie
                  aux_threads=0, raster_axes=None, raster_group=None, raster_orient="m"),)
 
 
-def array_sum_scalar(n: int = 1 << 24, grid: int = 1024, block: int = 256, copies: int = 2, ident: str = "r_sum_16m_scalar") -> dict:
+def array_sum_scalar(n: int = 1 << 24, grid: int = 2048, block: int = 256, copies: int = 2, ident: str = "r_sum_16m_scalar") -> dict:
     """The array sum as emmy writes it, before any regrouping: scalar loads strided over the block's threads, x seen as
     [grid, n / grid] (one row per block), then the same form over the partials."""
     assert n % grid == 0 and (n // grid) % (copies * block) == 0

@@ -349,7 +349,25 @@ def match_attention(src, strict: bool) -> Plan:
 GELU_OPS = ["multiply", "multiply", "multiply", "multiply", "add", "multiply", "tanh", "add", "multiply", "multiply"]
 
 
-def match_mlp(src, strict: bool) -> Plan:
+MLP_CLUSTER = 8            # CTAs per cluster of the fused MLP template
+MLP_FUSED_MAX_COLS = 256   # columns of y one CTA can hold in tensor memory beside two accumulators of a hidden chunk
+MLP_FUSED_CLUSTERS = 16    # clusters launched (128 of the 148 SMs: a cluster of 8 must sit inside one GPC)
+
+
+def mlp_fused_refusal(T: int, D: int, Hd: int):
+    """Why the cluster-fused MLP template does not fit these sizes (None: it fits)."""
+    C = MLP_CLUSTER
+    if D % (16 * C) or D // C > MLP_FUSED_MAX_COLS:
+        return (f"d_model {D} over a cluster of {C}: {D / C:g} columns of y per CTA (a multiple of 16, at most {MLP_FUSED_MAX_COLS}: "
+                "y's f32 accumulators must fit the tensor memory of the cluster beside the hidden chunk's)")
+    if D % 64:
+        return f"d_model {D} is not a multiple of the 64-element K-slice"
+    if Hd % (128 * C):
+        return f"hidden {Hd} is not a multiple of {128 * C} (a chunk of 128 units per CTA and round)"
+    return None
+
+
+def match_mlp(src, strict: bool, disable=frozenset()) -> Plan:
     """y = (gelu_tanh((x . w1) s1) . w2) s2 in emmy's column-recomputing form (examples/k_gelu_mlp/
     k_matmul_reduce_6918c9.ir.txt, tests/kernels.py:99-122): thread (row, column, lane) walks the hidden
     units lane, lane + L, ..., recomputes h = x[row, :] . w1[:, unit] for each (the work the reference's cluster
@@ -430,16 +448,48 @@ def match_mlp(src, strict: bool) -> Plan:
 
     e = src.name
     s1_buf, s2_buf = scalars[s1[0]], scalars[s2[0]]
+    sig = codegen.signature(src)
+    decode = ['#include "emb_dequant.cuh"',
+              f'extern "C" __global__ void __launch_bounds__(256) {e}__w1(const unsigned char* __restrict__ codes, __nv_bfloat16* __restrict__ out) {{',
+              f"    emb::dequant_transpose_e4m3(codes, out, {D}, {Hd});", "}",
+              f'extern "C" __global__ void __launch_bounds__(256) {e}__w2(const unsigned char* __restrict__ codes, __nv_bfloat16* __restrict__ out) {{',
+              f"    emb::dequant_transpose_e4m3(codes, out, {Hd}, {D});", "}"]
+    pre = [
+        dict(entry=f"{e}__w1", grid=[math.ceil(D / 64) * math.ceil(Hd / 64), 1, 1], block=[256, 1, 1], cluster=1, smem_bytes=0,
+             params=[dict(kind="buffer", name=lw.input), dict(kind="scratch", name="w1t", bytes=Hd * D * 2)]),
+        dict(entry=f"{e}__w2", grid=[math.ceil(Hd / 64) * math.ceil(D / 64), 1, 1], block=[256, 1, 1], cluster=1, smem_bytes=0,
+             params=[dict(kind="buffer", name=lw2.input), dict(kind="scratch", name="w2t", bytes=D * Hd * 2)]),
+    ]
+    fused_why = "disabled" if "dsmem" in disable else mlp_fused_refusal(T, D, Hd)
+    if fused_why is None:
+        C, ncols = MLP_CLUSTER, D // MLP_CLUSTER
+        tiles = math.ceil(T / 128)
+        clusters = min(tiles, MLP_FUSED_CLUSTERS)
+        smem = 7 * 32768 + 1024 + 256
+        lines = ['#include "emb_mlp_fused.cuh"', *decode,
+                 f'extern "C" __global__ void __cluster_dims__({C}, 1, 1) __launch_bounds__(256, 1) {e}({sig}, '
+                 "const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w1t, "
+                 "const __grid_constant__ CUtensorMap tmap_w2t, unsigned* __restrict__ status) {",
+                 f"    emb::mlp_fused_kernel<{C}, {ncols}>(&tmap_x, &tmap_w1t, &tmap_w2t, p_{w.output}, emb::MlpShape{{{T}, {D}, {Hd}}}, "
+                 f"p_{s1_buf}, p_{s2_buf}, status);", "}"]
+        extra = [tmap("x", lx.input, "bf16", (D, T), (D * 2,), (64, 128)), tmap("w1t", "w1t", "bf16", (D, Hd), (D * 2,), (64, 128)),
+                 tmap("w2t", "w2t", "bf16", (Hd, D), (Hd * 2,), (64, ncols)), dict(kind="status", name="status")]
+        remarks = [f"MLP template, fused in clusters of {C}: {T} tokens, d_model {D}, hidden {Hd}; a cluster owns 128 token rows, every CTA "
+                   f"the f32 accumulators of {ncols} columns of y in tensor memory; per round each CTA computes one chunk of 128 hidden "
+                   "units (tcgen05, tanh-GELU on the way out of tensor memory, bf16 into its own shared memory) and gathers the other "
+                   f"{C - 1} chunks from its peers' shared memory (mapa + ld.shared::cluster) for y += h_j w2_j: the hidden activations "
+                   "never leave the cluster",
+                   f"three launches from one module: {e}__w1, {e}__w2 (e4m3 -> bf16 decode, K-major), {e} ({clusters} clusters x {C} CTAs "
+                   f"of 256 threads, {smem} B of shared memory each); scratch: {(2 * Hd * D * 2) >> 20} MiB (the decoded weights; no h)",
+                   "cluster-wide hand-offs on mbarriers with remote arrivals and bounded waits (no barrier.cluster inside the loop)"]
+        return Plan("clusters", "\n".join(lines) + "\n", remarks, grid=clusters * C, block=256, cluster=C, smem_bytes=smem,
+                    extra_params=extra, pre=pre)
+
     stage = (128 + 256) * 64 * 2
     smem = GEMM_STAGES * stage + 1024 + 256
     tiles1 = math.ceil(T / 128) * math.ceil(Hd / 256)
     tiles2 = math.ceil(T / 128) * math.ceil(D / 256)
-    sig = codegen.signature(src)
-    lines = ['#include "emb_gemm.cuh"', '#include "emb_dequant.cuh"',
-             f'extern "C" __global__ void __launch_bounds__(256) {e}__w1(const unsigned char* __restrict__ codes, __nv_bfloat16* __restrict__ out) {{',
-             f"    emb::dequant_transpose_e4m3(codes, out, {D}, {Hd});", "}",
-             f'extern "C" __global__ void __launch_bounds__(256) {e}__w2(const unsigned char* __restrict__ codes, __nv_bfloat16* __restrict__ out) {{',
-             f"    emb::dequant_transpose_e4m3(codes, out, {Hd}, {D});", "}",
+    lines = ['#include "emb_gemm.cuh"', *decode,
              f'extern "C" __global__ void __launch_bounds__(192, 1) {e}__h(const __grid_constant__ CUtensorMap tmap_x, '
              "const __grid_constant__ CUtensorMap tmap_w1t, __nv_bfloat16* __restrict__ h, const float* __restrict__ scale, "
              "unsigned* __restrict__ status) {",
@@ -449,15 +499,10 @@ def match_mlp(src, strict: bool) -> Plan:
              "const __grid_constant__ CUtensorMap tmap_w2t, unsigned* __restrict__ status) {",
              f"    emb::gemm_tn_kernel<{GEMM_STAGES}, {GEMM_GROUP_M}, true, emb::EPI_SCALE>(&tmap_h, &tmap_w2t, p_{w.output}, "
              f"emb::GemmShape{{{T}, {D}, {Hd}}}, status, p_{s2_buf});", "}"]
-    pre = [
-        dict(entry=f"{e}__w1", grid=[math.ceil(D / 64) * math.ceil(Hd / 64), 1, 1], block=[256, 1, 1], cluster=1, smem_bytes=0,
-             params=[dict(kind="buffer", name=lw.input), dict(kind="scratch", name="w1t", bytes=Hd * D * 2)]),
-        dict(entry=f"{e}__w2", grid=[math.ceil(Hd / 64) * math.ceil(D / 64), 1, 1], block=[256, 1, 1], cluster=1, smem_bytes=0,
-             params=[dict(kind="buffer", name=lw2.input), dict(kind="scratch", name="w2t", bytes=D * Hd * 2)]),
+    pre.append(
         dict(entry=f"{e}__h", grid=[min(TARGET_SMS, tiles1), 1, 1], block=[192, 1, 1], cluster=1, smem_bytes=smem,
              params=[tmap("x", lx.input, "bf16", (D, T), (D * 2,), (64, 128)), tmap("w1t", "w1t", "bf16", (D, Hd), (D * 2,), (64, 256)),
-                     dict(kind="scratch", name="h", bytes=T * Hd * 2), dict(kind="buffer", name=s1_buf), dict(kind="status", name="status")]),
-    ]
+                     dict(kind="scratch", name="h", bytes=T * Hd * 2), dict(kind="buffer", name=s1_buf), dict(kind="status", name="status")]))
     extra = [tmap("h", "h", "bf16", (Hd, T), (Hd * 2,), (64, 128)), tmap("w2t", "w2t", "bf16", (Hd, D), (Hd * 2,), (64, 256)),
              dict(kind="status", name="status")]
     remarks = [f"MLP template: {T} tokens, d_model {D}, hidden {Hd}; the e4m3 weights are decoded once to bf16 (exactly) and "
@@ -465,7 +510,6 @@ def match_mlp(src, strict: bool) -> Plan:
                "epilogue (h kept in bf16), y = s2 h w2",
                f"four launches from one module: {e}__w1, {e}__w2 (decode), {e}__h ({tiles1} tiles), {e} ({tiles2} tiles); "
                f"scratch: {(2 * Hd * D * 2 + T * Hd * 2) >> 20} MiB",
-               "the recomputation of h by every (column, lane) thread of the IR is shared by construction; the cluster / "
-               "shared-memory exchange of the reference's rewrite is not used (h goes through L2 / HBM once)"]
+               f"not fused in a cluster: {fused_why}; h makes one bf16 round trip through L2 / HBM between the two matmuls"]
     return Plan("clusters", "\n".join(lines) + "\n", remarks, grid=min(TARGET_SMS, tiles2), block=192, smem_bytes=smem,
                 extra_params=extra, pre=pre)

@@ -30,12 +30,12 @@ def reference(host):
     return g @ w2
 
 
-@pytest.mark.parametrize("tokens,d_model,hidden", [(128, 256, 256), (256, 512, 1024), (200, 264, 328)])
+@pytest.mark.parametrize("tokens,d_model,hidden", [(128, 256, 256), (256, 512, 1152), (200, 264, 328)])
 def test_mlp_small_against_the_oracle(tmp_path, tokens, d_model, hidden):
     block = 64
     p = problems.gelu_mlp(tokens=tokens, d_model=d_model, hidden=hidden, lanes=8, block=block, ident="t")
     prob = runner.Problem(problems.write(p, tmp_path), "optimized")
-    assert prob.kernels[0].launch_info["family"] == "clusters" and len(prob.launches) == 4
+    assert prob.kernels[0].launch_info["family"] == "clusters" and len(prob.launches) == 4  # decode x 2, two matmuls
     got = prob.run()["mlp"]
     grid = p["kernels"][0]["grid"]
     blocks = sorted(set(np.random.default_rng(3).integers(0, grid, 48).tolist()) | {0, grid - 1})
@@ -44,6 +44,41 @@ def test_mlp_small_against_the_oracle(tmp_path, tokens, d_model, hidden):
     # bf16 output of sums of O(100) terms: well inside the fp8 tolerance; the measured margin is far below 1
     assert check(got.reshape(-1)[cells], want[cells]) < 0.5
     check(got, reference(prob.host))
+
+
+@pytest.mark.parametrize("tokens,d_model,hidden", [(256, 512, 1024), (128, 128, 1024), (200, 1024, 2048), (384, 2048, 2048),
+                                                   (128 * 19, 256, 2048)])
+def test_mlp_fused_in_clusters_against_the_oracle(tmp_path, tokens, d_model, hidden):
+    """The cluster-fused template (hidden chunks exchanged through distributed shared memory): 64, 16, 128 and 256
+    columns of y per CTA, one and two rounds of chunks, token rows past the end of the last tile, and more token
+    tiles than clusters (a cluster then reuses its tensor memory and barriers for a second tile). Checked against
+    the oracle on sampled CTAs, against the f64 expression everywhere, and against the two-matmul chain of the same
+    problem; a second launch must find every barrier, the tensor memory and the peers as the first one did."""
+    block = 64
+    p = problems.gelu_mlp(tokens=tokens, d_model=d_model, hidden=hidden, lanes=8, block=block, ident="t")
+    folder = problems.write(p, tmp_path)
+    prob = runner.Problem(folder, "optimized", canary=True)
+    info = prob.kernels[0].launch_info
+    assert info["family"] == "clusters" and info["cluster"] == 8 and len(prob.launches) == 3  # decode x 2, one fused kernel
+    assert "ld.shared::cluster" in prob.kernels[0].ptx and "tcgen05.mma" in prob.kernels[0].ptx
+    got = prob.run()["mlp"]
+    prob.check_canaries()
+    grid = p["kernels"][0]["grid"]
+    blocks = sorted(set(np.random.default_rng(3).integers(0, grid, 12).tolist()) | {0, grid - 1})
+    want = oracle_problem(p, prob.host, blocks=blocks)["mlp"].reshape(-1)
+    cells = np.concatenate([np.arange(b * block // 8, (b + 1) * block // 8) for b in blocks])
+    assert check(got.reshape(-1)[cells], want[cells]) < 0.5
+    check(got, reference(prob.host))
+    again = prob.run()["mlp"]
+    assert np.array_equal(again.view(np.uint16), got.view(np.uint16))
+    import os
+    os.environ["EMMY_PTX_DISABLE"] = "dsmem"
+    try:
+        chain = runner.Problem(folder, "optimized")
+    finally:
+        del os.environ["EMMY_PTX_DISABLE"]
+    assert len(chain.launches) == 4
+    assert check(got, chain.run()["mlp"].astype(np.float64)) < 0.5
 
 
 def test_mlp_statement_lowering_matches_too(tmp_path):
