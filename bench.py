@@ -92,12 +92,21 @@ WORKLOADS = {
     # regroup rewrite deals 16-byte chunks to the threads
     "sum_scalar": dict(folder="r_sum_16m_scalar", bound="hbm", dominant=0, dtype="f32", work=_sum_work, sizes=dict(n=1 << 24),
                        describe="f32 array sum of 2^24 in emmy's scalar spelling, regrouped into 16-byte chunks"),
+    # a mid-size MLP whose d_model fits the cluster-fused template (EMMY_PTX_PREFER=dsmem), as the default two-matmul
+    # chain and fused: the measured reason why the chain is the default
+    "mlp_2048": dict(folder="k_mlp_gelu_tanh_16384x2048x8192", bound="tensor", dominant=2, dtype="bf16", work=_mlp_work,
+                     sizes=dict(tokens=16384, d_model=2048, hidden=8192),
+                     describe="GELU MLP 16384x2048x8192 as decode + two tcgen05 matmuls (the default)"),
+    "mlp_2048_fused": dict(folder="k_mlp_gelu_tanh_16384x2048x8192", bound="tensor", dominant=2, dtype="bf16", prefer="dsmem",
+                           work=lambda k: dict(flops=2 * _mlp_work(k)["flops"]), sizes=dict(tokens=16384, d_model=2048, hidden=8192),
+                           describe="GELU MLP 16384x2048x8192 fused in clusters of 8 (hidden chunks through distributed shared memory)"),
     # the matmul handed over as a warp-level mma.sync schedule (fragment form) plus its fold kernel: optimized mode proves
     # it a matmul and runs the tcgen05 template, --mode plain runs the schedule as written
     "fragments": dict(folder="m_f16_8192_fragments", bound="tensor", dominant=0, dtype="f16", work=_matmul_work, oracle="fragment",
                       describe="f16 GEMM 8192^3 given in fragment form (mma.sync schedule, B stored N x K) + fold kernel"),
 }
-DEFAULT_FAMILIES = "sum,softmax,matmul,attention,elementwise,elementwise_add,sum_scalar,fragments"
+CHUNKED = ("mlp", "matmul", "attention", "fragments")  # e2e in slices of the units (pipeline.ChunkedProblem)
+DEFAULT_FAMILIES = "sum,softmax,matmul,attention,elementwise,elementwise_add,sum_scalar,fragments,mlp_2048,mlp_2048_fused"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel at the one-GPU size, from the ncu
 # captures summarised under profiles/ (None until captured)
 NCU_TRAFFIC = {"softmax": 212.3e6, "sum": 67.5e6, "matmul": 1253.1e6, "attention": 1056.2e6, "mlp": 1723.4e6, "fragments": 1326.0e6}
@@ -178,7 +187,7 @@ def _oracle_share(blocks):
 def full_problem(workload: str) -> tuple:
     """(the authored problem at the one-GPU size, the arguments of its kernels from meta.json)."""
     from emmy_ptx import problems
-    p = problems.WORKLOADS[workload]()
+    p = problems.WORKLOADS[workload.replace("_fused", "")]()
     meta = json.loads((PKG / "problems" / WORKLOADS[workload]["folder"] / "meta.json").read_text())
     return p, meta["kernels"]
 
@@ -204,10 +213,10 @@ def oracle_sample(workload: str, budget_s: float, workers: int, host: dict | Non
         host = {}
         for km in meta_args:
             host.update(runner.host_inputs(km["args"]))
-    if workload == "mlp":
+    if workload.startswith("mlp"):
         # one CTA of the full problem walks 2048 hidden units of 4096-long dot products per thread: minutes in the
         # interpreter. Its cost is linear in the hidden units (every trip runs the same statements), so the sample is a
-        # CTA of the same IR on the first 256 hidden units of the same weights, scaled by 16384 / 256.
+        # CTA of the same IR on the first 256 hidden units of the same weights, scaled by hidden / 256.
         from emmy_ptx import problems
         full_hidden, cut = host["w1"].shape[1], 256
         p = problems.gelu_mlp(tokens=host["x"].shape[0], d_model=host["x"].shape[1], hidden=cut)
@@ -295,7 +304,7 @@ def f64_sample(workload: str, host: dict, budget_s: float = 3.0) -> dict | None:
         qq, kk, vv = t64(q[:pairs]), t64(k[:pairs]), t64(v[:pairs])
         return timed(lambda: torch.nn.functional.scaled_dot_product_attention(qq, kk, vv, is_causal=True), pairs, q.shape[0],
                      "(batch, head) pairs")
-    if workload == "mlp":
+    if workload.startswith("mlp"):
         rows = 128
         x = t64(host["x"][:rows])
         w1, w2 = t64(host["w1"]) * float(host["w1_scale"][0]), t64(host["w2"]) * float(host["w2_scale"][0])
@@ -348,7 +357,7 @@ def main() -> None:
     import numpy as np
     import torch
     import torch.distributed as dist
-    from emmy_ptx import driver, multi, problems, runner
+    from emmy_ptx import driver, multi, pipeline, problems, runner
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -389,7 +398,14 @@ def main() -> None:
         w = WORKLOADS[workload]
         p_full, meta_full = full_problem(workload)
         if "sizes" in w:  # measured on one GPU only
-            prob = runner.Problem(PKG / "problems" / w["folder"], args.mode, device=local)
+            prefer = os.environ.get("EMMY_PTX_PREFER")
+            if w.get("prefer"):
+                os.environ["EMMY_PTX_PREFER"] = w["prefer"]
+            try:
+                prob = runner.Problem(PKG / "problems" / w["folder"], args.mode, device=local)
+            finally:
+                if w.get("prefer"):
+                    os.environ.pop("EMMY_PTX_PREFER") if prefer is None else os.environ.update(EMMY_PTX_PREFER=prefer)
             return prob, dict(w["sizes"]), None, prob.host
         pl = multi.plan(workload, rank, world)
         kw = dict(multi.FULL_SIZES[workload], **pl["kwargs"])
@@ -529,12 +545,22 @@ def main() -> None:
         # rows are independent in a row-wise kernel: the public API pipelines slices of rows (copy in, launch, copy out on a
         # few streams) so that both directions of the host link and the GPU work at once
         pipelined = prob.rows_pipeline(chunks=8, streams=4)
+        chunked = None
+        if pipelined is None and pl is not None and workload in CHUNKED and exchange is None:
+            # several launches, tensor maps: the same overlap by compiling the rank's share in four slices of its units
+            try:
+                chunked = pipeline.ChunkedProblem(workload, kw, prob.host, args.mode, local, chunks=4, streams=3, root=scratch_root)
+            except Exception as e:  # noqa: BLE001 - the plain sequence below still measures the call
+                chunked = None
+                timing["chunked_e2e_unavailable"] = f"{type(e).__name__}: {e}"[:200]
         barrier()
         for i in range(2 + reps):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             if pipelined is not None:
                 pipelined(pinned, out_host)
+            elif chunked is not None:
+                chunked.run(pinned, out_host)
             else:
                 for n, t in pinned.items():
                     ins[n].copy_(t, non_blocking=True)
@@ -549,8 +575,12 @@ def main() -> None:
         e2e = dict(value=all_max(statistics.mean(times)), unit="us", h2d_bytes_per_step=int(all_sum(h2d)), d2h_bytes_per_step=int(all_sum(d2h)),
                    resident=resident,
                    how=("8 row slices on 4 streams: copy in, launch, copy out overlap" if pipelined is not None else
+                        "4 slices of the units, each compiled for its size, on 3 streams: copy in, launches, copy out overlap; "
+                        "preparation of resident operands (weight decode) once per step" if chunked is not None else
                         "copy in, launches, copy out on one stream") + "; bytes are the sum over ranks")
-        del pinned, out_host
+        if chunked is not None:
+            chunked.check_status()
+        del pinned, out_host, chunked
         return dict(prob=prob, kw=kw, pl=pl, host=full_host, mean_us=mean_us, timing=timing, roofline=roof, e2e=e2e,
                     aggregate=aggregate)
 

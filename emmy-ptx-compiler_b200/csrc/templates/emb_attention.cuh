@@ -35,14 +35,19 @@ namespace emb {
 
 struct AttnShape {
     int batch_heads;   // batch * heads
-    int seq;           // queries = keys per (batch, head); a multiple of 128
+    int seq;           // queries = keys per (batch, head); any count: a partial last tile's key slots score -inf
+                       // (as the reference fills the slots past the end of its last key block, emmy_ptx/mapping.py:743-754)
     float scale_log2;  // softmax scale * log2(e)
+    float inv_scale;   // 1 / softmax scale (used with a mask only)
 };
 
-template <int NQ, bool CAUSAL, bool BF16, int POLY_PERIOD>
+// The tensor maps are three-dimensional, (d, row of the head, head): rows past the end of a head read as zeros,
+// never as the next head's rows. MASKED: `mask` holds one f32 per key, added to every query's scaled score of
+// that key before the softmax (emmy's additive mask, tests/test_gpu_lowering.py:256-306 of the reference).
+template <int NQ, bool CAUSAL, bool BF16, int POLY_PERIOD, bool MASKED = false>
 __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restrict__ map_q, const CUtensorMap* __restrict__ map_k,
                                                      const CUtensorMap* __restrict__ map_v, void* __restrict__ o_out,
-                                                     AttnShape shape, unsigned* status) {
+                                                     AttnShape shape, unsigned* status, const float* __restrict__ mask = nullptr) {
     constexpr int BM = 128, BN = 128, D = 128, UMMA_K = 16;
     constexpr uint32_t HALF_BYTES = 128 * 64 * 2;     // a 128-row x 64-column 16-bit box: 16 KB
     constexpr uint32_t TILE_BYTES = 2 * HALF_BYTES;   // 128 x 128: 32 KB
@@ -76,21 +81,23 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
     const tc::Guard guard{status, abort_flag};
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int q_blocks = shape.seq / (NQ * BM);
+    const int q_blocks = (shape.seq + NQ * BM - 1) / (NQ * BM);
+    const int kv_tiles = (shape.seq + BN - 1) / BN;
     const int num_items = shape.batch_heads * q_blocks;
     unsigned* work_counter = status + 4;  // zero at launch; the last CTA to finish resets it (and status[5])
 
     // an item: NQ query tiles of one (batch, head); within a head the block with the most keys comes first
     struct Item {
-        int q0, row_base, n_kv[NQ], n_max;
+        int q0, bh, row_base, n_kv[NQ], n_max;
     };
     auto decode = [&](int w) {
         Item it;
         const int bh = w / q_blocks, qb = q_blocks - 1 - (w % q_blocks);
         it.q0 = qb * NQ * BM;
+        it.bh = bh;
         it.row_base = bh * shape.seq;
 #pragma unroll
-        for (int i = 0; i < NQ; ++i) it.n_kv[i] = CAUSAL ? (it.q0 + i * BM + BM) / BN : shape.seq / BN;
+        for (int i = 0; i < NQ; ++i) it.n_kv[i] = CAUSAL ? min(kv_tiles, (it.q0 + i * BM + BM) / BN) : kv_tiles;
         it.n_max = it.n_kv[NQ - 1];
         return it;
     };
@@ -144,12 +151,12 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
                     tc::mbar_arrive_expect_tx(&k_full[s], TILE_BYTES);
 #pragma unroll
                     for (int h = 0; h < 2; ++h)
-                        tc::tma_load_2d(k_smem + s * TILE_BYTES + h * HALF_BYTES, map_k, &k_full[s], h * 64, item.row_base + j * BN);
+                        tc::tma_load_3d(k_smem + s * TILE_BYTES + h * HALF_BYTES, map_k, &k_full[s], h * 64, j * BN, item.bh);
                     if (!tc::mbar_wait(&v_empty[s], ph ^ 1, guard, tc::WAIT_SMEM_EMPTY, 1000 + j)) { alive = false; break; }
                     tc::mbar_arrive_expect_tx(&v_full[s], TILE_BYTES);
 #pragma unroll
                     for (int h = 0; h < 2; ++h)
-                        tc::tma_load_2d(v_smem + s * TILE_BYTES + h * HALF_BYTES, map_v, &v_full[s], h * 64, item.row_base + j * BN);
+                        tc::tma_load_3d(v_smem + s * TILE_BYTES + h * HALF_BYTES, map_v, &v_full[s], h * 64, j * BN, item.bh);
                     if (j == 0) {  // Q after the first K and V: its buffer frees last (the previous item's last Q K^T)
                         if (!tc::mbar_wait(q_empty, (it & 1) ^ 1, guard, tc::WAIT_SMEM_EMPTY, 9000)) { alive = false; break; }
                         tc::mbar_arrive_expect_tx(q_full, NQ * TILE_BYTES);
@@ -157,8 +164,7 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
                         for (int i = 0; i < NQ; ++i)
 #pragma unroll
                             for (int h = 0; h < 2; ++h)
-                                tc::tma_load_2d(q_smem + i * TILE_BYTES + h * HALF_BYTES, map_q, q_full, h * 64,
-                                                item.row_base + item.q0 + i * BM);
+                                tc::tma_load_3d(q_smem + i * TILE_BYTES + h * HALF_BYTES, map_q, q_full, h * 64, item.q0 + i * BM, item.bh);
                     }
                 }
                 if (!alive) break;
@@ -279,9 +285,22 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
                     break;
                 }
                 tc::tc_fence_after_sync();
-                const bool diagonal = CAUSAL && j == n_mine - 1;  // keys beyond the query are masked
-                const int limit = q_row - j * BN;                 // on the diagonal tile columns <= limit are visible
+                // keys beyond the query (causal) or beyond the end of the head (a partial last tile) score -inf: on such a
+                // tile only columns <= limit are visible
+                const int past_end = shape.seq - 1 - j * BN;
+                const bool diagonal = (CAUSAL && j == n_mine - 1) || past_end < BN - 1;
+                const int limit = CAUSAL ? min(q_row - j * BN, past_end) : past_end;
                 uint32_t sr[2][32];                               // two chunks of 32 scores: one in use, one in flight
+                // with a mask: score + mask / scale here, so that (score * scale + mask) comes out of the scaling below
+                auto add_mask = [&](uint32_t(&cur)[32], int c) {
+                    if (MASKED) {
+#pragma unroll
+                        for (int x = 0; x < 32; ++x) {
+                            const int key = min(j * BN + c * 32 + x, shape.seq - 1);
+                            cur[x] = __float_as_uint(fmaf(__ldg(mask + key), shape.inv_scale, __uint_as_float(cur[x])));
+                        }
+                    }
+                };
                 // pass 1: the row maximum (eight independent chains, the next chunk's TMEM load in flight)
                 float mx8[8];
 #pragma unroll
@@ -292,6 +311,7 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
                     tc::tmem_ld_wait();
                     if (c + 1 < 4) tc::tmem_ld_32x32(s_addr + (c + 1) * 32, sr[(c + 1) & 1]);
                     uint32_t(&cur)[32] = sr[c & 1];
+                    add_mask(cur, c);
                     if (diagonal) {
 #pragma unroll
                         for (int x = 0; x < 32; ++x)
@@ -336,6 +356,7 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
                     tc::tmem_ld_wait();
                     if (c + 1 < 4) tc::tmem_ld_32x32(s_addr + (c + 1) * 32, sr[(c + 1) & 1]);
                     uint32_t(&cur)[32] = sr[c & 1];
+                    add_mask(cur, c);
                     if (diagonal) {
 #pragma unroll
                         for (int x = 0; x < 32; ++x)
@@ -390,6 +411,7 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
                     uint32_t orow[32];
                     tc::tmem_ld_32x32(o_addr + c * 32, orow);
                     tc::tmem_ld_wait();
+                    if (q_row >= shape.seq) continue;  // a row past the end of the head (partial last query tile)
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         uint4 v;

@@ -53,6 +53,14 @@ enum GemmEpilogue : int {
     EPI_SCALE_GELU = 2,  // c = gelu_tanh(acc * scale[0])
 };
 
+// A per-cell epilogue given by the caller: f(acc, row, column) -> value (the statements an IR has between its
+// contraction loop and its Write, lowered one by one). The default does nothing.
+struct NoCellEpilogue {
+    __device__ __forceinline__ float operator()(float acc, int, int) const { return acc; }
+};
+template <class F> struct HasCellEpilogue { static constexpr bool value = true; };
+template <> struct HasCellEpilogue<NoCellEpilogue> { static constexpr bool value = false; };
+
 template <int EPI> __device__ __forceinline__ float gemm_epilogue(float acc, float scale) {
     if (EPI == EPI_SCALE) return acc * scale;
     if (EPI == EPI_SCALE_GELU) return gelu_tanh_fast(acc * scale);
@@ -64,10 +72,11 @@ template <int EPI> __device__ __forceinline__ float gemm_epilogue(float acc, flo
 // 16-bit kind, the operand type).
 // B_NMAJOR: B is stored [K, N] (N contiguous) instead of [N, K]: its stage is four boxes of 64 columns x 64 k, read
 // through an MN-major descriptor. OUT_F32: C is f32 (the partial slabs of a split-K schedule) instead of 16-bit.
-template <int STAGES, int GROUP_M, bool BF16, int EPI = EPI_NONE, bool FP8 = false, bool B_NMAJOR = false, bool OUT_F32 = false>
+template <int STAGES, int GROUP_M, bool BF16, int EPI = EPI_NONE, bool FP8 = false, bool B_NMAJOR = false, bool OUT_F32 = false,
+          class CellEpilogue = NoCellEpilogue>
 __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ map_a, const CUtensorMap* __restrict__ map_b,
                                                void* __restrict__ c_out, GemmShape shape, unsigned* status,
-                                               const float* __restrict__ scale_ptr = nullptr) {
+                                               const float* __restrict__ scale_ptr = nullptr, CellEpilogue cell = CellEpilogue()) {
     constexpr int ELEM = FP8 ? 1 : 2;                       // bytes per operand element
     constexpr int BM = 128, BN = 256, BK = 128 / ELEM, UMMA_K = 32 / ELEM;  // a stage row and an MMA step are 128 and 32 bytes
     constexpr uint32_t A_BYTES = BM * BK * ELEM, B_BYTES = BN * BK * ELEM, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -211,6 +220,11 @@ __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ m
                     for (int x = 0; x < 32; ++x) r[x] = __float_as_uint(gemm_epilogue<EPI>(__uint_as_float(r[x]), scale));
                 }
                 const int col = tn * BN + cb;
+                if (HasCellEpilogue<CellEpilogue>::value && row < shape.m) {
+#pragma unroll
+                    for (int x = 0; x < 32; ++x)
+                        if (col + x < shape.n) r[x] = __float_as_uint(cell(__uint_as_float(r[x]), row, col + x));
+                }
                 if (OUT_F32) {
                     if (row < shape.m) {
                         float* dst = static_cast<float*>(c_out) + (static_cast<size_t>(slab) * shape.m + row) * shape.n + col;
@@ -271,10 +285,10 @@ __device__ __forceinline__ void gemm_tn_kernel(const CUtensorMap* __restrict__ m
 //             accumulator-empty barrier (8 arrivals)
 //
 // The tensor maps must have boxes of 128 rows for A and for B.
-template <int STAGES, int GROUP_M, bool BF16, int EPI = EPI_NONE, bool FP8 = false>
+template <int STAGES, int GROUP_M, bool BF16, int EPI = EPI_NONE, bool FP8 = false, class CellEpilogue = NoCellEpilogue>
 __device__ __forceinline__ void gemm_tn_pair_kernel(const CUtensorMap* __restrict__ map_a, const CUtensorMap* __restrict__ map_b,
                                                     void* __restrict__ c_out, GemmShape shape, unsigned* status,
-                                                    const float* __restrict__ scale_ptr = nullptr) {
+                                                    const float* __restrict__ scale_ptr = nullptr, CellEpilogue cell = CellEpilogue()) {
     constexpr int ELEM = FP8 ? 1 : 2;
     constexpr int BM = 256, BN = 256, HALF = 128, BK = 128 / ELEM, UMMA_K = 32 / ELEM;
     constexpr uint32_t A_BYTES = HALF * BK * ELEM, B_BYTES = HALF * BK * ELEM, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -405,6 +419,11 @@ __device__ __forceinline__ void gemm_tn_pair_kernel(const CUtensorMap* __restric
                     for (int x = 0; x < 32; ++x) r[x] = __float_as_uint(gemm_epilogue<EPI>(__uint_as_float(r[x]), scale));
                 }
                 const int col = tn * BN + cb;
+                if (HasCellEpilogue<CellEpilogue>::value && row < shape.m) {
+#pragma unroll
+                    for (int x = 0; x < 32; ++x)
+                        if (col + x < shape.n) r[x] = __float_as_uint(cell(__uint_as_float(r[x]), row, col + x));
+                }
                 if (row < shape.m) {
                     out_t* dst = c + static_cast<size_t>(row) * shape.n + col;
                     if (vec_ok && col + 32 <= shape.n) {

@@ -336,11 +336,12 @@ __device__ __forceinline__ void mlp_fused_kernel(const CUtensorMap* __restrict__
                     if (alive) {
                         const uint32_t src = tc::smem_of_cta(h_own, (rank + j) % C);
                         uint8_t* dst = h_stage + slot * CHUNK;
-#pragma unroll 4
-                        for (int i = 0; i < static_cast<int>(CHUNK / 16 / 128); ++i) {
-                            const uint32_t off = (i * 128 + tid) * 16;
-                            *reinterpret_cast<uint4*>(dst + off) = mlpf::ld_cluster_16(src + off);
-                        }
+                        constexpr int PIECES = static_cast<int>(CHUNK / 16 / 128);  // 16 per thread: all loads in flight, then the stores
+                        uint4 piece[PIECES];
+#pragma unroll
+                        for (int i = 0; i < PIECES; ++i) piece[i] = mlpf::ld_cluster_16(src + (i * 128 + tid) * 16);
+#pragma unroll
+                        for (int i = 0; i < PIECES; ++i) *reinterpret_cast<uint4*>(dst + (i * 128 + tid) * 16) = piece[i];
                         tc::fence_async_smem();
                         __syncwarp();
                         if (lane == 0) tc::mbar_arrive(&hs_full[slot]);

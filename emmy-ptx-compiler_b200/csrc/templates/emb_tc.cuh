@@ -61,7 +61,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // A wait gives up after this long on the global nanosecond timer (looked at every 256 polls): far
 // beyond any legitimate wait of these kernels, which run for milliseconds as a whole.
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+// (EMB_WAIT_LIMIT_NS, given to the compiler, sets another limit: a test of the time-out itself uses milliseconds.)
+#ifndef EMB_WAIT_LIMIT_NS
+#define EMB_WAIT_LIMIT_NS 2000000000ull
+#endif
+constexpr uint64_t WAIT_LIMIT_NS = EMB_WAIT_LIMIT_NS;
 
 __device__ __forceinline__ uint64_t global_ns() {
     uint64_t t;

@@ -133,6 +133,12 @@ class Launch:
                 self._slots[i] = ctypes.addressof(cell)
         self.desc = LaunchDesc(fn.handle, (ctypes.c_uint32 * 3)(*grid), (ctypes.c_uint32 * 3)(*block), int(cluster),
                                int(smem_bytes), ctypes.cast(self._slots, ctypes.POINTER(ctypes.c_void_p)), n, int(flags))
+        self.buffers: list = []  # names of the buffers the launch reads or writes (filled by who binds it)
+        self.scratch: list = []  # keys of its scratch buffers
+
+    def scratch_names(self) -> set:
+        """The bare names of the launch's scratch buffers (a tensor map over a scratch buffer names it so)."""
+        return {key.split(".", 1)[1] for key in self.scratch}
 
 
 def _chain(launches):

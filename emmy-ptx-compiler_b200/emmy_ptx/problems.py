@@ -211,6 +211,36 @@ def matmul_f16(m: int = 8192, n: int = 8192, k: int = 8192, block: int = 256, dt
                          "b": dict(dtype=dtype, shape=[n, k], seed=1, dist="normal", scale=scale)})
 
 
+def matmul_bias_relu(m: int = 512, n: int = 512, k: int = 256, block: int = 256, dtype: str = "f16", b_layout: str = "nk",
+                     ident: str = "m_bias_relu"):
+    """C = relu(A B^T + bias) * gain: the matmul with statements between its loop and its Write (a bias row, an activation,
+    a scalar), and with B stored [N, K] (``b_layout="nk"``) or [K, N] (``"kn"``)."""
+    assert (m * n) % block == 0 and b_layout in ("nk", "kn")
+    b_index = (V("a1"), V("a2")) if b_layout == "nk" else (V("a2"), V("a1"))
+    loop = Loop(axis=Axis(name="a2", extent=k), body=(
+        Load(names=("in0",), input="a", index=(V("a0"), V("a2")), dtype=None),
+        Load(names=("in1",), input="b", index=b_index, dtype=None),
+        Assign(name="v0", op="multiply", args=("in0", "in1"), dtype=F32),
+        Accum(name="acc0", value="v0", op="add", dtype=F32, axes=("a2",), base=None)), unroll=False, seed=True)
+    epilogue = (Load(names=("bv",), input="bias", index=(V("a1"),), dtype=F32),
+                Load(names=("gn",), input="gain", index=(I(0),), dtype=F32),
+                Assign(name="z", op="add", args=("acc0", "bv"), dtype=F32),
+                Assign(name="r", op="relu", args=("z",), dtype=F32),
+                Assign(name="y", op="multiply", args=("r", "gn"), dtype=F32))
+    store = Write(output="matmul", index=(V("a0"), V("a1")), values=("y",), value_dtype=F32)
+    body = (Tile(axes=(Axis(name="a0", extent=m), Axis(name="a1", extent=n)), body=(loop, *epilogue, store), block_threads=block,
+                 aux_threads=0, raster_axes=None, raster_group=None, raster_orient="m"),)
+    kern = dict(node="matmul", entry="k_matmul_bias_relu", body=body, grid=m * n // block, block=block,
+                inputs=["gain", "a", "b", "bias"], output=("matmul", [m, n], dtype), final=True)
+    scale = 1.0 / math.sqrt(k)
+    return dict(id=ident, code="torch.relu(a @ b.T + bias) * 1.5", rtol=2e-3, atol=2e-3, graph_inputs=["a", "b", "bias"],
+                graph_outputs=["matmul"], kernels=[kern],
+                tensors={"a": dict(dtype=dtype, shape=[m, k], seed=0, dist="normal", scale=scale),
+                         "b": dict(dtype=dtype, shape=[n, k] if b_layout == "nk" else [k, n], seed=1, dist="normal", scale=scale),
+                         "bias": dict(dtype="f32", shape=[n], seed=2, dist="normal", scale=0.5),
+                         "gain": dict(dtype="f32", shape=[1], data=[1.5], constant=1.5)})
+
+
 def matmul_fp8_body(m: int, n: int, k: int, block: int):
     """C = (A . B^T) * scale with A [m, k] and B [n, k] e4m3 codes: decode, f32 products, f32 sum, one scale."""
     loop = Loop(axis=Axis(name="a2", extent=k), body=(
@@ -242,19 +272,26 @@ def matmul_fp8(m: int = 8192, n: int = 8192, k: int = 8192, block: int = 256, id
 # ---------------------------------------------------------------- cfg 4: causal attention, online softmax
 
 
-def attention_body(batch: int, heads: int, seq: int, dim: int, scale: float, causal: bool = True):
+def attention_body(batch: int, heads: int, seq: int, dim: int, scale: float, causal: bool = True, mask: bool = False,
+                   scale_as: str = "let"):
     """One block per (batch, head, query): thread c holds output column c; every thread of the block
     computes the row's scores (the work a template shares), emmy's fused form
-    (examples/a01_attention/k_matmul_softmax_reduce_b55365.ir.txt, tests/test_oracle.py:214-231)."""
+    (examples/a01_attention/k_matmul_softmax_reduce_b55365.ir.txt, tests/test_oracle.py:214-231). ``mask`` adds a
+    per-key f32 value to the scaled score (tests/test_gpu_lowering.py:256-306); ``scale_as="reciprocal"`` spells
+    the scale as emmy does after splitting a source division: the reciprocal of the constant ``div_c1``."""
     bhq = (V("a0"), V("a1"), V("a2"))
     dot = Loop(axis=Axis(name="a5", extent=dim), body=(
         Load(names=("qv",), input="q", index=(*bhq, V("a5")), dtype=None),
         Load(names=("kv",), input="k", index=(V("a0"), V("a1"), V("a4"), V("a5")), dtype=None),
         Assign(name="p", op="multiply", args=("qv", "kv"), dtype=F32),
         Accum(name="dot", value="p", op="add", dtype=F32, axes=("a5",), base=None)), unroll=False, seed=True)
+    score = ((Assign(name="s", op="multiply", args=("dot", "scale"), dtype=F32),) if not mask else
+             (Assign(name="s0", op="multiply", args=("dot", "scale"), dtype=F32),
+              Load(names=("mk",), input="mask", index=(V("a4"),), dtype=F32),
+              Assign(name="s", op="add", args=("s0", "mk"), dtype=F32)))
     update = (
         dot,
-        Assign(name="s", op="multiply", args=("dot", "scale"), dtype=F32),
+        *score,
         Assign(name="gn", op="maximum", args=("m", "s"), dtype=F32),
         Assign(name="dg", op="subtract", args=("m", "gn"), dtype=F32),
         Assign(name="alpha", op="exp", args=("dg",), dtype=F32),
@@ -271,7 +308,12 @@ def attention_body(batch: int, heads: int, seq: int, dim: int, scale: float, cau
     )
     keys = StridedLoop(axis=Axis(name="a4", extent=seq), start=I(0), step=I(1), body=update, unroll=False,
                        end=B("+", V("a2"), I(1)) if causal else None, seed=True)
-    stmts = (Let(name="scale", value=Literal(value=float(scale), dtype="float"), dtype=F32),
+    if scale_as == "let":
+        named = (Let(name="scale", value=Literal(value=float(scale), dtype="float"), dtype=F32),)
+    else:
+        named = (Load(names=("dc",), input="div_c1", index=(I(0),), dtype=F32),
+                 Assign(name="scale", op="reciprocal", args=("dc",), dtype=F32))
+    stmts = (*named,
              Let(name="one", value=Literal(value=1.0, dtype="float"), dtype=F32),
              keys,
              Assign(name="inv", op="reciprocal", args=("l",), dtype=F32),
@@ -284,15 +326,20 @@ def attention_body(batch: int, heads: int, seq: int, dim: int, scale: float, cau
 
 
 def attention(batch: int = 8, heads: int = 32, seq: int = 4096, dim: int = 128, causal: bool = True,
-              dtype: str = "f16", ident: str = "a_f16_causal_8x32x4096x128"):
+              dtype: str = "f16", mask: bool = False, scale_as: str = "let", ident: str = "a_f16_causal_8x32x4096x128"):
     import numpy as np
     scale = float(np.float32(1.0 / math.sqrt(dim)))
     shape = [batch, heads, seq, dim]
-    kern = dict(node="attn", entry="k_attention", body=attention_body(batch, heads, seq, dim, scale, causal),
-                grid=batch * heads * seq, block=dim, inputs=["q", "k", "v"], output=("attn", shape, dtype), final=True)
+    extra = (["mask"] if mask else []) + (["div_c1"] if scale_as == "reciprocal" else [])
+    kern = dict(node="attn", entry="k_attention", body=attention_body(batch, heads, seq, dim, scale, causal, mask, scale_as),
+                grid=batch * heads * seq, block=dim, inputs=[*extra, "q", "k", "v"], output=("attn", shape, dtype), final=True)
+    tensors = {n: dict(dtype=dtype, shape=shape, seed=i, dist="normal") for i, n in enumerate("qkv")}
+    if mask:  # a tenth of the keys far below every score; the tests overwrite it to mask whole tiles
+        tensors["mask"] = dict(dtype="f32", shape=[seq], seed=7, dist="normal", scale=1.0)
+    if scale_as == "reciprocal":
+        tensors["div_c1"] = dict(dtype="f32", shape=[1], data=[math.sqrt(dim)], constant=math.sqrt(dim))
     return dict(id=ident, code="torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=%s)" % causal,
-                rtol=2e-3, atol=2e-3, graph_inputs=["q", "k", "v"], graph_outputs=["attn"], kernels=[kern],
-                tensors={n: dict(dtype=dtype, shape=shape, seed=i, dist="normal") for i, n in enumerate("qkv")})
+                rtol=2e-3, atol=2e-3, graph_inputs=["q", "k", "v"], graph_outputs=["attn"], kernels=[kern], tensors=tensors)
 
 
 # ---------------------------------------------------------------- cfg 5: fused tanh-GELU MLP, bf16 x, e4m3 weights
@@ -503,7 +550,8 @@ def matmul_fragments(m: int = 8192, n: int = 8192, k: int = 8192, ident: str = "
 
 WORKLOADS = {"sum": array_sum, "softmax": row_softmax, "matmul": matmul_f16, "attention": attention, "mlp": gelu_mlp,
              "fragments": matmul_fragments, "elementwise": bias_gelu, "elementwise_add": bias_relu_residual,
-             "sum_scalar": array_sum_scalar}
+             "sum_scalar": array_sum_scalar,
+             "mlp_2048": lambda **kw: gelu_mlp(**{**dict(tokens=16384, d_model=2048, hidden=8192, ident="k_mlp_gelu_tanh_16384x2048x8192"), **kw})}
 
 
 def write_all(root) -> list:

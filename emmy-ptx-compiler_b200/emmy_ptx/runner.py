@@ -156,7 +156,12 @@ class CompiledKernel:
                 else:
                     raise ValueError(f"unknown parameter kind {p['kind']!r}")
             flags = driver.LAUNCH_PDL if li.get("pdl") else 0
-            return driver.Launch(fn, li["grid"], li["block"], li.get("cluster", 1), li.get("smem_bytes", 0), params, flags)
+            launch = driver.Launch(fn, li["grid"], li["block"], li.get("cluster", 1), li.get("smem_bytes", 0), params, flags)
+            # what the launch touches, by name: lets a host tell parameter preparation (reads only the job's resident
+            # operands, writes scratch) from the launches that depend on a step's inputs
+            launch.buffers = [p["name"] for p in li["params"] if p["kind"] == "buffer"] + [p["buffer"] for p in li["params"] if p["kind"] == "tmap"]
+            launch.scratch = [f"{entry}.{p['name']}" for p in li["params"] if p["kind"] == "scratch"]
+            return launch
 
         li = self.launch_info
         # scratch must exist before a tensor map over it is built: make them in the order the header lists them
@@ -189,8 +194,10 @@ class Problem:
 
     GUARD_BYTES = 4096
 
-    def __init__(self, folder, mode: str = "optimized", device: int = 0, inputs: dict | None = None, scratch: dict | None = None,
+    def __init__(self, folder, mode: str = "optimized", device: int = 0, inputs: dict | None = None, share: dict | None = None,
                  exchange=None, canary: bool = False):
+        """``inputs``: name -> numpy array instead of the seeded draws of meta.json. ``share``: name -> device tensor to bind
+        instead of making one (an operand or a scratch buffer, ``"<entry>.<name>"``, that several problems use)."""
         import torch
         self.folder = Path(folder)
         self.meta = json.loads((self.folder / "meta.json").read_text())
@@ -212,6 +219,11 @@ class Problem:
                 self.dtypes.setdefault(name, a["dtype"])
                 if name in self.tensors:
                     continue
+                if share and name in share:
+                    self.tensors[name] = share[name]
+                    if not (a.get("output") or a.get("intermediate")):
+                        self.host[name] = given[name]
+                    continue
                 if a.get("output") or a.get("intermediate"):
                     shape = a["shape"] or [1]
                     dtype = getattr(torch, TORCH_DTYPE[a["dtype"]])
@@ -222,6 +234,8 @@ class Problem:
                 else:
                     self.host[name] = given[name]
                     self.tensors[name] = to_torch(given[name], a["dtype"], self.device)
+        for name, t in (share or {}).items():  # shared scratch: found by bind() under its "<entry>.<name>" key
+            self.tensors.setdefault(name, t)
         self.exchange = exchange
         if exchange is not None:
             self.tensors[EXCHANGE] = exchange.record

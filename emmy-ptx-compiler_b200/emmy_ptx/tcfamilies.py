@@ -92,13 +92,18 @@ def gemm_geometry(M: int, N: int, elem_bytes: int = 2) -> dict:
 
 
 def match_matmul(src, strict: bool) -> Plan:
+    """C = epilogue(A B^T): one thread per cell, a serial contraction loop of f32 products, then optionally Loads
+    and Assigns that make the written value from the sum (a bias row, an activation, a scale: what emmy fuses behind
+    a matmul), then one Write. B may be stored [N, K] (column-major B) or [K, N] (row-major B: read through an
+    MN-major descriptor). The epilogue statements are lowered one by one, with the statement lowering's own rules,
+    into a per-cell function the template calls between tensor memory and the store."""
     tile = single_tile(src)
     need(len(tile.axes) == 2, "the Tile is not over (row, column) cells")
     m_axis, n_axis = tile.axes[0].name, tile.axes[1].name
     M, N = tile.axes[0].extent.as_static(), tile.axes[1].extent.as_static()
     body = list(tile.body)
-    need(len(body) == 2 and kind(body[0]) == "Loop" and kind(body[1]) == "Write", "the cell is not one loop and one Write")
-    loop, write = body
+    need(len(body) >= 2 and kind(body[0]) == "Loop" and kind(body[-1]) == "Write", "the cell is not a loop, ..., one Write")
+    loop, epilogue, write = body[0], body[1:-1], body[-1]
     k_axis, K = loop.axis.name, loop.axis.extent.as_static()
     need(loop.seed and len(loop.body) == 4 and [kind(s) for s in loop.body] == ["Load", "Load", "Assign", "Accum"],
          "the loop is not Load, Load, multiply, Accum")
@@ -108,43 +113,97 @@ def match_matmul(src, strict: bool) -> Plan:
          "the product is not an f32 multiply of the two loads")
     need(acc.value == mul.name and acc.base is None and codegen.CANON.get(acc.op.name) == "add"
          and dtype_name(acc.dtype) in (None, "f32"), "the accumulator is not an f32 sum of the products")
-    # which load is the row operand?
-    def operand(load, axis):
-        return len(load.index) == 2 and is_var(load.index[0], axis) and is_var(load.index[1], k_axis)
-    if operand(la, m_axis) and operand(lb, n_axis):
-        a, b = la, lb
-    elif operand(lb, m_axis) and operand(la, n_axis):
-        a, b = lb, la
+
+    def indexed(load, first, second):
+        return len(load.index) == 2 and is_var(load.index[0], first) and is_var(load.index[1], second)
+    a = next((ld for ld in (la, lb) if indexed(ld, m_axis, k_axis)), None)
+    need(a is not None, "no operand is read as A[row, k]")
+    b = lb if a is la else la
+    if indexed(b, n_axis, k_axis):
+        b_kn = False
+    elif indexed(b, k_axis, n_axis):
+        b_kn = True
     else:
-        raise Refusal("the operands are not A[row, k] and B[column, k] (row-major A, column-major B)")
+        raise Refusal("the other operand is neither B[column, k] nor B[k, column]")
     A, B, C = src.buffers.get(a.input), src.buffers.get(b.input), src.buffers.get(write.output)
     need(A is not None and B is not None and C is not None, "unknown buffers")
     need(A.dtype == B.dtype and A.dtype in ("f16", "bf16"), "the operands are not both f16 or both bf16")
     need(C.dtype == A.dtype, "the output type differs from the operands'")
-    need(tuple(A.shape) == (M, K) and tuple(B.shape) == (N, K) and tuple(C.shape) == (M, N), "buffer shapes do not fit the cells")
+    need(tuple(A.shape) == (M, K) and tuple(B.shape) == ((K, N) if b_kn else (N, K)) and tuple(C.shape) == (M, N),
+         "buffer shapes do not fit the cells")
     need(a.input not in src.written and b.input not in src.written, "the kernel writes an operand")
-    need(tuple(write.values) == (acc.name,) and not write.atomic and len(write.index) == 2
-         and is_var(write.index[0], m_axis) and is_var(write.index[1], n_axis), "the Write is not C[row, column] = acc")
+    need(not write.atomic and len(write.values) == 1 and len(write.index) == 2
+         and is_var(write.index[0], m_axis) and is_var(write.index[1], n_axis), "the Write is not C[row, column] = one value")
+    # the epilogue: per-cell statements that may read the sum, the cell's coordinates and read-only buffers
+    inner = {la.names[0], lb.names[0], mul.name, k_axis}
+    made = {acc.name}
+    for st in epilogue:
+        k = kind(st)
+        need(k in ("Load", "Assign", "Let"), f"a {k} between the loop and the Write")
+        if k == "Load":
+            need(st.input in src.buffers and st.input not in src.written, "the epilogue loads from a buffer the kernel writes")
+            used = set().union(*[ir_vars(e) for e in st.index]) if st.index else set()
+            made.update(st.names)
+        elif k == "Assign":
+            used = set(st.args)
+            made.add(st.name)
+        else:
+            used = ir_vars(st.value)
+            made.add(st.name)
+        need(not (used & inner), "the epilogue reads a value of the loop's last trip")
+        need(not (used & {"lane", "warp"}), "the epilogue reads lane or warp (the template re-deals the cells)")
+    need(write.values[0] in made, "the written value is made neither by the loop nor by the epilogue")
+    need(epilogue or write.values[0] == acc.name, "the Write is not C[row, column] = acc")
     need(not strict, "the tensor cores sum a K-slice in their own order (--strict keeps the IR's)")
-    need(K % 8 == 0, "the row stride of the operands is not a multiple of 16 bytes (K % 8)")
+    need(K % 8 == 0 and (not b_kn or N % 8 == 0), "a row stride of an operand is not a multiple of 16 bytes")
     need(M * N >= 128 * 256 // 4, "too small for a 128 x 256 tensor-core tile")
 
     bf16 = A.dtype == "bf16"
     g = gemm_geometry(M, N)
-    call = [f"    emb::{g['kernel']}<{g['stages']}, {g['group']}, {str(bf16).lower()}>(&tmap_a, &tmap_b, p_{write.output}, "
-            f"emb::GemmShape{{{M}, {N}, {K}}}, status);"]
+    if b_kn:  # the MN-major read exists on lone CTAs only
+        tiles = math.ceil(M / 128) * math.ceil(N / 256)
+        stage = (128 + 256) * 128
+        g = dict(kernel="gemm_tn_kernel", stages=GEMM_STAGES, group=GEMM_GROUP_M, b_rows=256, tiles=tiles, tile="128 x 256",
+                 grid=min(TARGET_SMS, tiles), cluster=1, stage=stage, smem=GEMM_STAGES * stage + 1024 + 256, how="persistent CTAs")
+    pre_lines, cell = [], ""
+    if epilogue or write.values[0] != acc.name:
+        em = codegen.Emitter(src, plain=False, strict=False)
+        em.depth = 2
+        em.emit(f"{em.var(m_axis, 'i64')} = row_; {em.var(n_axis, 'i64')} = col_; {em.var(acc.name, 'f32')} = acc_;")
+        em.facts[m_axis] = em.facts[n_axis] = None
+        for st in epilogue:
+            getattr(em, "s_" + kind(st))(st)
+        code, dt = em.use(write.values[0])
+        em.emit(f"return {em.convert(code, dt, 'f32')};")
+        decls = [f"    {codegen.CTYPE[d]} v_{n} = emb::zero<{codegen.CTYPE[d]}>();" for n, d in em.vars.items() if n not in ("lane", "warp")]
+        pre_lines = decls + ["    auto cell_ = [&](float acc_, int row_, int col_) -> float {"] + em.lines + ["    };"]
+        cell = ", nullptr, cell_"
+    lone = g["kernel"] == "gemm_tn_kernel"
+    flags = f"{str(bf16).lower()}, emb::EPI_NONE, false" + (f", {str(b_kn).lower()}, false" if lone else "") + (", decltype(cell_)" if cell else "")
+    call = pre_lines + [f"    emb::{g['kernel']}<{g['stages']}, {g['group']}, {flags}>(&tmap_a, &tmap_b, p_{write.output}, "
+                        f"emb::GemmShape{{{M}, {N}, {K}}}, status{cell});"]
     extra_sig = ["const __grid_constant__ CUtensorMap tmap_a", "const __grid_constant__ CUtensorMap tmap_b",
                  "unsigned* __restrict__ status"]
-    source = wrapper(src, '#include "emb_gemm.cuh"', call, extra_sig, 192, cluster=g["cluster"])
-    extra = [tmap("a", a.input, A.dtype, (K, M), (K * 2,), (64, 128)),
-             tmap("b", b.input, B.dtype, (K, N), (K * 2,), (64, g["b_rows"])),
-             dict(kind="status", name="status")]
+    includes = '#include "emb_gemm.cuh"' + ("\n" + codegen.PRELUDE.split("\n", 1)[1] if cell else "")
+    source = wrapper(src, includes, call, extra_sig, 192, cluster=g["cluster"])
+    b_map = tmap("b", b.input, B.dtype, (N, K), (N * 2,), (64, 64)) if b_kn else tmap("b", b.input, B.dtype, (K, N), (K * 2,), (64, g["b_rows"]))
+    extra = [tmap("a", a.input, A.dtype, (K, M), (K * 2,), (64, 128)), b_map, dict(kind="status", name="status")]
     remarks = [f"tensor-core matmul template: {M} x {N} x {K} {A.dtype}, f32 accumulation in tensor memory; {g['tiles']} tiles of "
                f"{g['tile']} walked by {g['grid']} CTAs of 192 threads (TMA producer, tcgen05.mma issuer, 4 epilogue warps): {g['how']}",
                f"TMA tensor-map loads (128-byte swizzle, no multicast) into {g['stages']} stages of {g['stage']} B on mbarriers; "
                "two 256-column TMEM accumulators so that a tile's epilogue overlaps the next tile's MMAs",
                f"tile order: {g['group']} row-blocks share each B panel in L2"]
+    if b_kn:
+        remarks.append("B is stored [K, N]: its tiles are read through an MN-major shared-memory descriptor (four 64-column boxes per stage)")
+    if cell:
+        remarks.append(f"{len(epilogue)} statement(s) between the loop and the Write run per cell on the accumulator as it leaves tensor "
+                       "memory (lowered one by one, as the statement lowering would)")
     return Plan("tensorcore", source, remarks, grid=g["grid"], block=192, cluster=g["cluster"], smem_bytes=g["smem"], extra_params=extra)
+
+
+def ir_vars(e) -> set:
+    from . import ir
+    return ir.expr_vars(e)
 
 
 def match_matmul_e4m3(src, strict: bool) -> Plan:
@@ -215,7 +274,11 @@ def match_attention(src, strict: bool) -> Plan:
     tests/test_oracle.py:204-231): per (row, output column) thread a key loop that recomputes the row's
     score, then the online update gn = max(m, s), alpha = exp(m - gn), beta = exp(s - gn),
     l = alpha l + beta, o = alpha o + beta v, m = max(m, s); legality as emmy_ptx/mapping.py:413-467
-    (the update reads m before m moves, no two sums share an addend, the scores read no carried state)."""
+    (the update reads m before m moves, no two sums share an addend, the scores read no carried state).
+    Spellings taken: the scale as a literal Let or as the reciprocal of a constant (emmy's split of a source
+    division, ``reciprocal(div_c1)``); an additive per-key mask loaded between the scaling and the update
+    (tests/test_gpu_lowering.py:256-306); the key loop ending at ``query + 1`` (causal) or at the key count; any
+    key count (a partial last key tile scores -inf past the end, emmy_ptx/mapping.py:743-754)."""
     tile = single_tile(src)
     need(len(tile.axes) >= 2, "the Tile is not over (..., query, column) cells")
     lead = tile.axes[:-2]
@@ -223,8 +286,22 @@ def match_attention(src, strict: bool) -> Plan:
     S, D = tile.axes[-2].extent.as_static(), tile.axes[-1].extent.as_static()
     need(D == 128 and src.launch.block == D, "the head dimension (= block) is not 128")
     body = list(tile.body)
-    lets = {s.name: s for s in body if kind(s) == "Let"}
-    rest = [s for s in body if kind(s) != "Let"]
+    # constants named before the key loop: literal Lets, scalars loaded from ConstantOp buffers, reciprocals of those
+    consts, at = {}, 0
+    while at < len(body) and kind(body[at]) != "StridedLoop":
+        st = body[at]
+        k = kind(st)
+        if k == "Let" and kind(st.value) == "Literal":
+            consts[st.name] = float(st.value.value)
+        elif k == "Load" and len(st.names) == 1 and src.constants.get(st.input) is not None:
+            consts[st.names[0]] = float(src.constants[st.input])
+        elif k == "Assign" and st.op.name == "reciprocal" and len(st.args) == 1 and consts.get(st.args[0]):
+            import numpy as np
+            consts[st.name] = float(np.float32(1.0) / np.float32(consts[st.args[0]]))
+        else:
+            raise Refusal(f"a {k} before the key loop that does not name a constant")
+        at += 1
+    rest = body[at:]
     need(len(rest) == 4 and [kind(s) for s in rest] == ["StridedLoop", "Assign", "Assign", "Write"],
          "the cell is not key loop, reciprocal, multiply, Write")
     loop, inv, res, write = rest
@@ -260,22 +337,38 @@ def match_attention(src, strict: bool) -> Plan:
     else:
         raise Refusal("the score does not read Q[.., query, d] and K[.., key, d]")
     tail = lb_[1:]
+    for st in tail:  # constants may also be named inside the loop (the reference's test spells its scale there)
+        if kind(st) == "Let" and kind(st.value) == "Literal":
+            consts[st.name] = float(st.value.value)
+    tail = [st for st in tail if not (kind(st) == "Let" and kind(st.value) == "Literal")]
     stmts = {getattr(s, "name", None): s for s in tail if kind(s) == "Assign"}
     accums = [s for s in tail if kind(s) == "Accum"]
     loads = [s for s in tail if kind(s) == "Load"]
-    need(len(accums) == 3 and len(loads) == 1 and len(tail) == len(stmts) + 4, "the update is not three Accums around one Load of V")
+    need(len(accums) == 3 and len(loads) in (1, 2) and len(tail) == len(stmts) + 3 + len(loads), "the update is not three Accums around the Load of V")
     m_acc = tail[-1]
     need(kind(m_acc) == "Accum" and codegen.CANON.get(m_acc.op.name) == "maximum" and m_acc.base is None,
          "the maximum does not move last (the update must read m before it moves)")
     m, s_name = m_acc.name, m_acc.value
     sums = [a for a in accums if a is not m_acc]
     need(all(codegen.CANON.get(a.op.name) == "add" and a.base is not None for a in sums), "the sums are not rescaled sums")
-    s_st = _assign(stmts, s_name, "multiply")
+    # the score: dot * scale, optionally + mask[key]
+    s_st = _assign(stmts, s_name)
+    mask_load = None
+    if s_st.op.name == "add":
+        need(len(loads) == 2, "a score with an addend that is not a loaded mask")
+        mask_load = next((ld for ld in loads if ld.names[0] in s_st.args), None)
+        need(mask_load is not None and len(s_st.args) == 2, "a score with an addend that is not a loaded mask")
+        scaled = [a for a in s_st.args if a != mask_load.names[0]][0]
+        s_st = _assign(stmts, scaled, "multiply")
+        mbuf = src.buffers.get(mask_load.input)
+        need(mbuf is not None and mbuf.dtype == "f32" and tuple(mbuf.shape) == (S,) and len(mask_load.index) == 1
+             and is_var(mask_load.index[0], key_axis) and mask_load.input not in src.written, "the mask is not one f32 per key")
+    else:
+        need(s_st.op.name == "multiply" and len(loads) == 1, "the score is not the scaled dot product")
     need(dot.name in s_st.args, "the score is not the scaled dot product")
     scale_name = [a for a in s_st.args if a != dot.name]
-    need(len(scale_name) == 1 and scale_name[0] in lets and kind(lets[scale_name[0]].value) == "Literal"
-         and float(lets[scale_name[0]].value.value) > 0, "the scale is not a positive constant")
-    scale = float(lets[scale_name[0]].value.value)
+    need(len(scale_name) == 1 and consts.get(scale_name[0], 0.0) > 0, "the scale is not a positive constant")
+    scale = consts[scale_name[0]]
     # the two rescaling factors
     exps = [a for a in stmts.values() if a.op.name == "exp"]
     need(len(exps) == 2, "the update does not have exactly two exponentials")
@@ -288,7 +381,7 @@ def match_attention(src, strict: bool) -> Plan:
     alpha = next((e for e in exps if factor(e) == m), None)
     beta = next((e for e in exps if factor(e) == s_name), None)
     need(alpha is not None and beta is not None, "the factors are not exp(m - max) and exp(s - max)")
-    vload = loads[0]
+    vload = next(ld for ld in loads if ld is not mask_load)
     need(indexed(vload, key_axis, c_axis), "V is not read at [.., key, column]")
     l_acc = o_acc = None
     for a in sums:
@@ -300,8 +393,7 @@ def match_attention(src, strict: bool) -> Plan:
         if other == vload.names[0]:
             o_acc = a
         else:
-            need(other in lets and kind(lets[other].value) == "Literal" and float(lets[other].value.value) == 1.0,
-                 "the running sum's addend is not beta * 1")
+            need(consts.get(other) == 1.0, "the running sum's addend is not beta * 1")
             l_acc = a
     need(l_acc is not None and o_acc is not None and l_acc.value != o_acc.value, "no running sum and output pair (or a shared addend)")
     need(inv.op.name == "reciprocal" and tuple(inv.args) == (l_acc.name,) and res.op.name == "multiply"
@@ -316,31 +408,37 @@ def match_attention(src, strict: bool) -> Plan:
     need(dt in ("f16", "bf16") and all(b.dtype == dt for b in bufs), "Q, K, V, O are not all f16 or all bf16")
     need(not ({ql.input, kl.input, vload.input} & set(src.written)), "the kernel writes an operand")
     need(not strict, "the tensor cores and the per-tile softmax sum in their own order (--strict keeps the IR's)")
-    need(S % 128 == 0, "the sequence length is not a multiple of the 128-row tile")
+    need(S >= 1, "no keys")
 
     nq = 2 if S % 256 == 0 else 1
     bh = math.prod(a.extent.as_static() for a in lead) if lead else 1
-    items = bh * (S // (nq * 128))
+    items = bh * math.ceil(S / (nq * 128))
     grid = min(TARGET_SMS, items)
     threads = 64 + 128 * nq
     smem = (nq + 4) * 32768 + 1024 + 256
     scale_log2 = scale * math.log2(math.e)
-    call = [f"    emb::attention_fwd_kernel<{nq}, {str(causal).lower()}, {str(dt == 'bf16').lower()}, {ATTN_POLY_PERIOD}>(&tmap_q, &tmap_k, &tmap_v, "
-            f"p_{write.output}, emb::AttnShape{{{bh}, {S}, {codegen.c_float(scale_log2)}}}, status);"]
+    masked = mask_load is not None
+    call = [f"    emb::attention_fwd_kernel<{nq}, {str(causal).lower()}, {str(dt == 'bf16').lower()}, {ATTN_POLY_PERIOD}, {str(masked).lower()}>("
+            f"&tmap_q, &tmap_k, &tmap_v, p_{write.output}, emb::AttnShape{{{bh}, {S}, {codegen.c_float(scale_log2)}, {codegen.c_float(1.0 / scale)}}}, "
+            f"status{', p_' + mask_load.input if masked else ''});"]
     extra_sig = ["const __grid_constant__ CUtensorMap tmap_q", "const __grid_constant__ CUtensorMap tmap_k",
                  "const __grid_constant__ CUtensorMap tmap_v", "unsigned* __restrict__ status"]
     source = wrapper(src, '#include "emb_attention.cuh"', call, extra_sig, threads)
-    rows = bh * S
-    extra = [tmap("q", ql.input, dt, (D, rows), (D * 2,), (64, 128)), tmap("k", kl.input, dt, (D, rows), (D * 2,), (64, 128)),
-             tmap("v", vload.input, dt, (D, rows), (D * 2,), (64, 128)), dict(kind="status", name="status")]
+
+    def head_map(name, buffer):  # (d, row of the head, head): rows past the end of a head read as zeros
+        return tmap(name, buffer, dt, (D, S, bh), (D * 2, S * D * 2), (64, 128, 1))
+    extra = [head_map("q", ql.input), head_map("k", kl.input), head_map("v", vload.input), dict(kind="status", name="status")]
     remarks = [f"attention template: {bh} (batch, head) pairs x {S} queries, head dimension 128, {dt}, "
-               f"{'causal' if causal else 'full'}; {grid} persistent CTAs of {threads} threads claim {items} work items of {nq} query "
-               "tile(s) of 128 rows against 128-key tiles (scheduler + TMA producer, tcgen05.mma issuer, one softmax warp group "
-               "per query tile); the next item's loads and first scores overlap the previous item's epilogue",
+               f"{'causal' if causal else 'full'}{', additive per-key mask' if masked else ''}; {grid} persistent CTAs of {threads} threads claim "
+               f"{items} work items of {nq} query tile(s) of 128 rows against 128-key tiles (scheduler + TMA producer, tcgen05.mma issuer, "
+               "one softmax warp group per query tile); the next item's loads and first scores overlap the previous item's epilogue",
                "online softmax recognised (m, l, o with alpha = exp(m - max), beta = exp(s - max)); applied once per 128-key "
                "tile in base 2, O rescaled in tensor memory only when the maximum moves by more than 2^8",
                "S = Q K^T and O += P V on tcgen05.mma with S, P and O in tensor memory; K, V in two TMA stages each; "
                "the CTAs of one (batch, head) are neighbours so that K and V are shared in L2"]
+    if S % 128:
+        remarks.append(f"{S} keys are not a multiple of the 128-key tile: the last tile's slots past the end score -inf, its rows "
+                       "past the end are zeros (three-dimensional tensor maps) and are not stored")
     return Plan("blocking", source, remarks, grid=grid, block=threads, smem_bytes=smem, extra_params=extra)
 
 
@@ -352,6 +450,12 @@ GELU_OPS = ["multiply", "multiply", "multiply", "multiply", "add", "multiply", "
 MLP_CLUSTER = 8            # CTAs per cluster of the fused MLP template
 MLP_FUSED_MAX_COLS = 256   # columns of y one CTA can hold in tensor memory beside two accumulators of a hidden chunk
 MLP_FUSED_CLUSTERS = 16    # clusters launched (128 of the 148 SMs: a cluster of 8 must sit inside one GPC)
+
+
+def prefers(name: str) -> bool:
+    """Is the optional, not-by-default rewrite ``name`` asked for (EMMY_PTX_PREFER, a comma-separated list)?"""
+    import os
+    return name in {n.strip() for n in os.environ.get("EMMY_PTX_PREFER", "").split(",")}
 
 
 def mlp_fused_refusal(T: int, D: int, Hd: int):
@@ -460,7 +564,15 @@ def match_mlp(src, strict: bool, disable=frozenset()) -> Plan:
         dict(entry=f"{e}__w2", grid=[math.ceil(Hd / 64) * math.ceil(D / 64), 1, 1], block=[256, 1, 1], cluster=1, smem_bytes=0,
              params=[dict(kind="buffer", name=lw2.input), dict(kind="scratch", name="w2t", bytes=D * Hd * 2)]),
     ]
-    fused_why = "disabled" if "dsmem" in disable else mlp_fused_refusal(T, D, Hd)
+    if "dsmem" in disable:
+        fused_why = "disabled"
+    elif not prefers("dsmem"):
+        fused_why = ("it fits these sizes but is not the default: measured on B200 it is several times slower than the two-matmul "
+                     "chain (its operand rings, the chunk and the staging slots share 224 KB of shared memory, too little in flight "
+                     "for the TMA latency); EMMY_PTX_PREFER=dsmem selects it") if mlp_fused_refusal(T, D, Hd) is None else \
+            mlp_fused_refusal(T, D, Hd)
+    else:
+        fused_why = mlp_fused_refusal(T, D, Hd)
     if fused_why is None:
         C, ncols = MLP_CLUSTER, D // MLP_CLUSTER
         tiles = math.ceil(T / 128)

@@ -118,3 +118,65 @@ def test_attention_full_size_sampled_rows_and_cross_check():
         check(got[b:b + 1], ref, "f16-wide", f"8x32x4096x128 batch {b} vs f32 attention")
     # the first query of every (batch, head) attends to key 0 only: its output is V[.., 0, :] exactly
     assert np.array_equal(got[:, :, 0, :], prob.host["v"][:, :, 0, :])
+
+
+def f64_attention(host, causal, scale, mask=None):
+    q, k, v = (host[n].astype(np.float64) for n in "qkv")
+    s = np.einsum("bhqd,bhkd->bhqk", q, k) * scale
+    if mask is not None:
+        s = s + mask.astype(np.float64)
+    if causal:
+        n = s.shape[-1]
+        s = np.where(np.tril(np.ones((n, n), bool)), s, -np.inf)
+    w = np.exp(s - s.max(axis=-1, keepdims=True))
+    return np.einsum("bhqk,bhkd->bhqd", w / w.sum(axis=-1, keepdims=True), v)
+
+
+def ragged_rows(batch_heads: int, seq: int):
+    rows = sorted({r for r in (0, 1, 127, 128, 129, 255, 256, seq - 130, seq - 2, seq - 1) if 0 <= r < seq})
+    return [bh * seq + r for bh in sorted({0, batch_heads - 1}) for r in rows]
+
+
+@pytest.mark.parametrize("seq,causal", [(300, False), (300, True), (44, False), (448, True), (129, True)])
+def test_attention_with_a_partial_last_tile(tmp_path, seq, causal):
+    """Key (and query) counts that are no multiple of the 128-row tile: the slots past the end score -inf
+    (emmy_ptx/mapping.py:743-754 of the reference), rows past the end are zeros and are not stored (the output sits
+    between guard zones)."""
+    p = problems.attention(batch=1, heads=3, seq=seq, dim=128, causal=causal, ident="t")
+    prob = runner.Problem(problems.write(p, tmp_path), "optimized", canary=True)
+    assert prob.kernels[0].launch_info["family"] == "blocking"
+    got = prob.run()["attn"]
+    prob.check_canaries()
+    assert np.isfinite(got.astype(np.float32)).all()
+    blocks = ragged_rows(3, seq)
+    want = oracle_problem(p, prob.host, blocks=blocks)["attn"].reshape(-1, 128)
+    check(got.reshape(-1, 128)[blocks], want[blocks], "f16", f"ragged S={seq} causal={causal} sampled rows vs oracle")
+    check(got, f64_attention(prob.host, causal, float(np.float32(1 / np.sqrt(128)))), "f16", f"ragged S={seq} causal={causal} all rows vs f64")
+
+
+@pytest.mark.parametrize("seq,causal", [(256, False), (300, False), (384, True)])
+def test_attention_with_an_additive_mask_and_a_masked_tile(tmp_path, seq, causal):
+    """The reference's blocked-attention test (tests/test_gpu_lowering.py:256-306: softmax(q k^T * scale + mask) v with
+    scattered keys and ONE WHOLE key block masked by -1e4) on the template's shapes: 128-key tiles, so keys 128..255 are
+    the masked block; the scale spelled as the reciprocal of a division's constant."""
+    p = problems.attention(batch=1, heads=2, seq=seq, dim=128, causal=causal, mask=True, scale_as="reciprocal", ident="t")
+    folder = problems.write(p, tmp_path)
+    rng = np.random.default_rng(5)
+    host = {n: rng.standard_normal((1, 2, seq, 128)).astype(np.float16) for n in "qkv"}
+    mask = np.zeros(seq, np.float32)
+    mask[[3, 9, 40]] = -1e4
+    mask[128:256] = -1e4
+    if causal:
+        mask[0] = 0.0  # (the first query sees key 0 only)
+    host["mask"] = mask
+    host["div_c1"] = np.array([np.sqrt(128)], np.float32)
+    prob = runner.Problem(folder, "optimized", inputs=host, canary=True)
+    info = prob.kernels[0].launch_info
+    assert info["family"] == "blocking" and "mask" in [q.get("name") for q in info["params"]]
+    got = prob.run()["attn"]
+    prob.check_canaries()
+    blocks = ragged_rows(2, seq)
+    want = oracle_problem(p, host, blocks=blocks)["attn"].reshape(-1, 128)
+    check(got.reshape(-1, 128)[blocks], want[blocks], "f16", f"masked S={seq} causal={causal} sampled rows vs oracle")
+    scale = float(np.float32(1.0) / np.float32(np.sqrt(128)))
+    check(got, f64_attention(host, causal, scale, mask), "f16", f"masked S={seq} causal={causal} all rows vs f64")

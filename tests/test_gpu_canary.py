@@ -44,3 +44,31 @@ def test_matmul_on_cta_pairs_stays_inside(tmp_path, monkeypatch):
     got = prob.run()["matmul"]
     prob.check_canaries()
     assert not np.isnan(got.astype(np.float32)).any()
+
+
+@pytest.mark.parametrize("workload,sizes", [("mlp", dict(tokens=512, d_model=256, hidden=512)), ("matmul", dict(m=512, n=256, k=128)),
+                                             ("attention", dict(batch=2, heads=2, seq=256, dim=128))])
+def test_a_problem_run_in_slices_gives_the_whole_problems_output(tmp_path, workload, sizes):
+    """pipeline.ChunkedProblem: the units cut in four slices, each compiled for its size, copies and kernels on three
+    streams, the resident operands uploaded once and their preparation (the MLP's weight decode) run once per call.
+    Slices fall on tile boundaries, so the bits are the whole problem's."""
+    import torch
+    from emmy_ptx import multi, pipeline
+    kw = multi.plan(workload, 0, 1, sizes)["kwargs"]
+    whole_problem = problems.WORKLOADS[workload](ident="whole", **kw)
+    prob = runner.Problem(problems.write(whole_problem, tmp_path), "optimized")
+    out_name = whole_problem["kernels"][-1]["output"][0]
+    whole = prob.run()[out_name]
+    chunked = pipeline.ChunkedProblem(workload, dict(sizes), prob.host, "optimized", 0, chunks=4, streams=3, root=tmp_path / "slices")
+    if workload == "mlp":
+        assert len(chunked.prepare) == 2 and all(len(work) == 2 for _, _, work in chunked.parts)  # decode once, two matmuls per slice
+    pinned = {n: prob.tensors[n].cpu().pin_memory() for n in chunked.plans[0]["slices"]}
+    dev_out = prob.tensors[out_name]
+    host_out = {out_name: torch.zeros(dev_out.shape, dtype=dev_out.dtype).pin_memory()}
+    for _ in range(2):  # a second call reuses everything
+        host_out[out_name].zero_()
+        chunked.run(pinned, host_out)
+        torch.cuda.synchronize()
+        chunked.check_status()
+        got = runner.to_numpy(host_out[out_name], prob.dtypes[out_name])
+        assert np.array_equal(got.view(np.uint16), whole.view(np.uint16))

@@ -72,3 +72,51 @@ def test_ranks_on_several_gpus_agree_bit_for_bit(tmp_path):
                         "--master-port", "29517", str(HERE / "exchange_worker.py"), str(folder), "6"],
                        capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0 and "exchange ok" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
+
+
+def test_a_tensor_core_templates_wait_gives_up_and_reports():
+    """The bounded mbarrier wait every tensor-core template uses (csrc/templates/emb_tc.cuh: mbar_wait), made to run
+    out on purpose and harmlessly: a barrier nobody arrives on, a limit of 20 ms instead of 2 s. The waiting thread
+    must come back with `false`, the status word must carry (code, CTA, step), the CTA's abort flag must make a later
+    wait return at once, the host must turn the word into EmbError(-3), and the context must be alive afterwards."""
+    import time
+
+    import torch
+    from emmy_ptx import driver, runner, toolchain
+    source = r'''
+#include "emb_tc.cuh"
+extern "C" __global__ void __launch_bounds__(64) k_wait_runs_out(unsigned* status) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        emb::tc::mbar_init(&bar, 1);
+        abort_flag = 0;
+        emb::tc::mbar_init_fence();
+    }
+    __syncthreads();
+    const emb::tc::Guard guard{status, &abort_flag};
+    if (threadIdx.x == 32) status[3] = emb::tc::mbar_wait(&bar, 0, guard, emb::tc::WAIT_TMEM_FULL, 77) ? 1u : 2u;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned long long t0 = emb::tc::global_ns();
+        status[6] = emb::tc::mbar_wait(&bar, 0, guard, emb::tc::WAIT_SMEM_FULL, 5) ? 1u : 2u;  // gives up at once: the CTA is aborting
+        status[7] = static_cast<unsigned>((emb::tc::global_ns() - t0) / 1000);
+    }
+}
+'''
+    ptx = toolchain.cuda_to_ptx(source, ("-DEMB_WAIT_LIMIT_NS=20000000ull",))
+    cubin, _ = toolchain.assemble(ptx)
+    driver.init(0)
+    fn = driver.Module(cubin).function("k_wait_runs_out")
+    status = torch.zeros(8, dtype=torch.int32, device="cuda")
+    t0 = time.time()
+    driver.launch([driver.Launch(fn, [3, 1, 1], [64, 1, 1], 1, 0, [status.data_ptr()])], torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 1.5
+    word = status.cpu().tolist()
+    assert word[0] == 3 and word[1] in (0, 1, 2) and word[2] == 77  # the first CTA to give up: accumulator never completed, step 77
+    assert word[3] == 2 and word[6] == 2 and word[7] < 5000          # both waits returned false, the second within microseconds
+    with pytest.raises(driver.EmbError) as err:
+        runner.raise_on_status("k_wait_runs_out", word)
+    assert err.value.code == -3 and "code 3" in str(err.value) and "step 77" in str(err.value)
+    assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0  # the context is alive

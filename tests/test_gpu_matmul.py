@@ -108,3 +108,27 @@ def test_e4m3_matmul_against_the_oracle(tmp_path, m, n, k):
     got = prob.run()["matmul"]
     want = oracle_problem(p, prob.host)["matmul"]
     check(got, want, "bf16")
+
+
+@pytest.mark.parametrize("m,n,k,b_layout,pairs", [(256, 512, 128, "nk", False), (200, 264, 72, "nk", False), (512, 768, 320, "nk", True),
+                                                   (256, 512, 128, "kn", False), (200, 264, 200, "kn", False)])
+def test_matmul_with_an_epilogue_and_either_b_layout(tmp_path, monkeypatch, m, n, k, b_layout, pairs):
+    """Statements between the contraction loop and the Write (bias row, relu, a scalar gain) run per cell on the
+    accumulator as it leaves tensor memory; B stored [K, N] is read through an MN-major descriptor. Lone CTAs, CTA
+    pairs, ragged shapes; against the oracle at the stated f16 tolerance."""
+    from emmy_ptx import tcfamilies
+    if pairs:
+        monkeypatch.setattr(tcfamilies, "GEMM_PAIR_MIN_TILES", 1)
+    block = 64 if (m * n) % 256 else 256
+    p = problems.matmul_bias_relu(m=m, n=n, k=k, block=block, b_layout=b_layout, ident="t")
+    prob = runner.Problem(problems.write(p, tmp_path), "optimized", canary=True)
+    info = prob.kernels[0].launch_info
+    assert info["family"] == "tensorcore" and info["cluster"] == (2 if pairs else 1)
+    got = prob.run()["matmul"]
+    prob.check_canaries()
+    want = oracle_problem(p, prob.host)["matmul"]
+    check(got, want, "f16", f"bias+relu {m}x{n}x{k} B {b_layout} vs oracle")
+    a, b = prob.host["a"].astype(np.float64), prob.host["b"].astype(np.float64)
+    ref = np.maximum(a @ (b.T if b_layout == "nk" else b) + prob.host["bias"].astype(np.float64), 0) * 1.5
+    check(got, ref, "f16")
+    assert (got == 0).mean() > 0.2  # the relu really cut something

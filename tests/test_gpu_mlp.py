@@ -30,7 +30,7 @@ def reference(host):
     return g @ w2
 
 
-@pytest.mark.parametrize("tokens,d_model,hidden", [(128, 256, 256), (256, 512, 1152), (200, 264, 328)])
+@pytest.mark.parametrize("tokens,d_model,hidden", [(128, 256, 256), (256, 512, 1024), (200, 264, 328)])
 def test_mlp_small_against_the_oracle(tmp_path, tokens, d_model, hidden):
     block = 64
     p = problems.gelu_mlp(tokens=tokens, d_model=d_model, hidden=hidden, lanes=8, block=block, ident="t")
@@ -48,7 +48,7 @@ def test_mlp_small_against_the_oracle(tmp_path, tokens, d_model, hidden):
 
 @pytest.mark.parametrize("tokens,d_model,hidden", [(256, 512, 1024), (128, 128, 1024), (200, 1024, 2048), (384, 2048, 2048),
                                                    (128 * 19, 256, 2048)])
-def test_mlp_fused_in_clusters_against_the_oracle(tmp_path, tokens, d_model, hidden):
+def test_mlp_fused_in_clusters_against_the_oracle(tmp_path, monkeypatch, tokens, d_model, hidden):
     """The cluster-fused template (hidden chunks exchanged through distributed shared memory): 64, 16, 128 and 256
     columns of y per CTA, one and two rounds of chunks, token rows past the end of the last tile, and more token
     tiles than clusters (a cluster then reuses its tensor memory and barriers for a second tile). Checked against
@@ -57,6 +57,7 @@ def test_mlp_fused_in_clusters_against_the_oracle(tmp_path, tokens, d_model, hid
     block = 64
     p = problems.gelu_mlp(tokens=tokens, d_model=d_model, hidden=hidden, lanes=8, block=block, ident="t")
     folder = problems.write(p, tmp_path)
+    monkeypatch.setenv("EMMY_PTX_PREFER", "dsmem")  # (the chain is the default: it is the faster one on this GPU)
     prob = runner.Problem(folder, "optimized", canary=True)
     info = prob.kernels[0].launch_info
     assert info["family"] == "clusters" and info["cluster"] == 8 and len(prob.launches) == 3  # decode x 2, one fused kernel
@@ -71,12 +72,8 @@ def test_mlp_fused_in_clusters_against_the_oracle(tmp_path, tokens, d_model, hid
     check(got, reference(prob.host))
     again = prob.run()["mlp"]
     assert np.array_equal(again.view(np.uint16), got.view(np.uint16))
-    import os
-    os.environ["EMMY_PTX_DISABLE"] = "dsmem"
-    try:
-        chain = runner.Problem(folder, "optimized")
-    finally:
-        del os.environ["EMMY_PTX_DISABLE"]
+    monkeypatch.delenv("EMMY_PTX_PREFER")
+    chain = runner.Problem(folder, "optimized")
     assert len(chain.launches) == 4
     assert check(got, chain.run()["mlp"].astype(np.float64)) < 0.5
 

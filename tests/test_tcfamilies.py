@@ -39,12 +39,12 @@ def test_matmul_refusals(tmp_path):
     src = load(tmp_path, problems.matmul_f16(m=256, n=512, k=128, ident="m"), "k_matmul")
     with pytest.raises(families.Refusal, match="own order"):
         tcfamilies.match_matmul(src, True)
-    # B indexed [k, n]: row-major B is not what the template loads
+    # B indexed [k, n] while the buffer is [N, K]: the index and the storage disagree
     def swap(b):
         loop = b[0]
         lb = loop.body[1]
         return [loop.replace(body=(loop.body[0], lb.replace(index=(lb.index[1], lb.index[0])), *loop.body[2:])), b[1]]
-    with pytest.raises(families.Refusal, match="row-major A, column-major B"):
+    with pytest.raises(families.Refusal, match="buffer shapes do not fit the cells"):
         tcfamilies.match_matmul(rebuilt(src, swap), False)
     # an f16 product (no dtype on the multiply) is not the f32 accumulation the tensor cores do
     def f16_product(b):
@@ -109,3 +109,27 @@ def test_tensor_maps_are_proved_on_the_host():
         args.update(bad)
         with pytest.raises(families.Refusal, match=why):
             tcfamilies.tmap(**args)
+
+
+def test_matmul_keeps_an_epilogue_and_takes_either_b_layout(tmp_path):
+    """The statements between the loop and the Write become a per-cell function of the template; B [K, N] is read
+    MN-major on lone CTAs; an epilogue that reads a value of the loop's last trip is refused."""
+    from emmy_ptx import frontend, problems, tcfamilies
+    from emmy_ptx.families import Refusal
+    from emmy_ptx.ir import Assign, datatype
+    import pytest
+    for layout in ("nk", "kn"):
+        folder = problems.write(problems.matmul_bias_relu(m=256, n=512, k=128, b_layout=layout, ident=layout), tmp_path)
+        src = frontend.load(folder / "k_matmul_bias_relu.ir.json")
+        plan = tcfamilies.match_matmul(src, False)
+        assert "auto cell_ = [&](float acc_, int row_, int col_) -> float {" in plan.source and "decltype(cell_)" in plan.source
+        assert ("MN-major" in " ".join(plan.remarks)) == (layout == "kn")
+        b_map = next(p for p in plan.extra_params if p.get("name") == "b")
+        assert b_map["box"] == ([64, 64] if layout == "kn" else [64, 256])
+    tile = src.body[0]
+    body = list(tile.body)
+    leak = Assign(name="z", op="add", args=("acc0", "in0"), dtype=datatype("f32"))
+    bad = frontend.KernelSource(src.name, (tile.replace(body=tuple([body[0], leak] + body[1:])),), src.params, src.buffers, src.launch,
+                                src.written, src.constants)
+    with pytest.raises(Refusal, match="last trip"):
+        tcfamilies.match_matmul(bad, False)
