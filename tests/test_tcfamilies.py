@@ -67,9 +67,18 @@ def test_attention_is_taken_and_refused(tmp_path):
     assert plan.block == 192 and "attention_fwd_kernel<1, false, false" in plan.source
     with pytest.raises(families.Refusal, match="own order"):
         tcfamilies.match_attention(src, True)
-    short = load(tmp_path, problems.attention(batch=1, heads=1, seq=96, dim=128, ident="c"), "k_attention")
-    with pytest.raises(families.Refusal, match="multiple of the 128-row tile"):
-        tcfamilies.match_attention(short, False)
+    # any key count is taken: a partial last tile, rows past the end read as zeros through three-dimensional tensor maps
+    short = load(tmp_path, problems.attention(batch=1, heads=3, seq=96, dim=128, ident="c"), "k_attention")
+    plan = tcfamilies.match_attention(short, False)
+    assert "attention_fwd_kernel<1, true, false" in plan.source and any("not a multiple of the 128-key tile" in r for r in plan.remarks)
+    maps = [q for q in plan.extra_params if q["kind"] == "tmap"]
+    assert all(q["dims"] == [128, 96, 3] and q["box"] == [64, 128, 1] and q["strides_bytes"] == [256, 96 * 256] for q in maps)
+    # an additive per-key mask and the scale as the reciprocal of a division's constant
+    masked = load(tmp_path, problems.attention(batch=1, heads=1, seq=256, dim=128, causal=False, mask=True, scale_as="reciprocal", ident="e"),
+                  "k_attention")
+    plan = tcfamilies.match_attention(masked, False)
+    assert "attention_fwd_kernel<2, false, false, 4, true>" in plan.source and ", p_mask);" in plan.source
+    assert "0.12751" in plan.source and "11.3137" in plan.source  # log2(e) / sqrt(128) and sqrt(128), from the constant's value
     narrow = load(tmp_path, problems.attention(batch=1, heads=1, seq=128, dim=64, ident="d"), "k_attention")
     with pytest.raises(families.Refusal, match="head dimension"):
         tcfamilies.match_attention(narrow, False)
