@@ -44,13 +44,21 @@ struct AttnShape {
 // The tensor maps are three-dimensional, (d, row of the head, head): rows past the end of a head read as zeros,
 // never as the next head's rows. MASKED: `mask` holds one f32 per key, added to every query's scaled score of
 // that key before the softmax (emmy's additive mask, tests/test_gpu_lowering.py:256-306 of the reference).
-template <int NQ, bool CAUSAL, bool BF16, int POLY_PERIOD, bool MASKED = false>
+// OPTIMISTIC: from an item's second key tile on, the tile's row maximum is not found by a pass of its own over the
+// scores in tensor memory: the weights are taken against the reference maximum carried from the earlier tiles while the
+// tile's own maximum is tracked, and the reference moves lazily before the NEXT tile (the final division by the
+// running sum makes any reference exact as long as nothing overflows). A score that exceeds the reference by more
+// than 2^15 - which would overflow a 16-bit weight - is caught chunk by chunk before its weight is made: the reference
+// then moves at once, and O, the running sum and the tile's weights not yet consumed are rescaled (rare, exact).
+// D: the head dimension, 128 or 64 (one or two 64-wide boxes per tile row).
+template <int NQ, bool CAUSAL, bool BF16, int POLY_PERIOD, bool MASKED = false, bool OPTIMISTIC = true, int D = 128>
 __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restrict__ map_q, const CUtensorMap* __restrict__ map_k,
                                                      const CUtensorMap* __restrict__ map_v, void* __restrict__ o_out,
                                                      AttnShape shape, unsigned* status, const float* __restrict__ mask = nullptr) {
-    constexpr int BM = 128, BN = 128, D = 128, UMMA_K = 16;
-    constexpr uint32_t HALF_BYTES = 128 * 64 * 2;     // a 128-row x 64-column 16-bit box: 16 KB
-    constexpr uint32_t TILE_BYTES = 2 * HALF_BYTES;   // 128 x 128: 32 KB
+    constexpr int BM = 128, BN = 128, UMMA_K = 16, HALVES = D / 64;
+    static_assert(D == 64 || D == 128, "head dimension 64 or 128");
+    constexpr uint32_t HALF_BYTES = 128 * 64 * 2;          // a 128-row x 64-column 16-bit box: 16 KB
+    constexpr uint32_t TILE_BYTES = HALVES * HALF_BYTES;   // 128 x D: 32 KB at D = 128
     constexpr int KV_STAGES = 2;
     constexpr uint32_t TMEM_COLS = 512;
     constexpr uint32_t S_COL = 0, O_COL = 256;  // S_i at i * 128, O_i at 256 + i * 128; P_i over S_i's first 64 columns
@@ -72,7 +80,8 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
     uint64_t* p_ready = s_full + 2;           // NQ
     uint64_t* o_done = p_ready + 2;           // NQ
     uint64_t* p_half = o_done + 2;            // NQ: the first 64 keys of P are written
-    uint64_t* q_empty = p_half + 2;           // 1: the item's last Q K^T has read the Q tiles
+    uint64_t* o_half = p_half + 2;            // NQ: the first half of P V of a key tile has completed
+    uint64_t* q_empty = o_half + 2;           // 1: the item's last Q K^T has read the Q tiles
     uint64_t* item_full = q_empty + 1;        // 2: a work item is published in the ring slot
     uint64_t* item_empty = item_full + 2;     // 2: every role has read it
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(item_empty + 2);
@@ -115,6 +124,7 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
             tc::mbar_init(&s_full[i], 1);
             tc::mbar_init(&p_ready[i], 4);  // one arrival per softmax warp
             tc::mbar_init(&p_half[i], 4);
+            tc::mbar_init(&o_half[i], 1);
             tc::mbar_init(&o_done[i], 1);
             tc::mbar_init(&item_full[i], 1);
             tc::mbar_init(&item_empty[i], 1 + 4 * NQ);  // the MMA thread and every softmax warp
@@ -150,12 +160,12 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
                     if (!tc::mbar_wait(&k_empty[s], ph ^ 1, guard, tc::WAIT_SMEM_EMPTY, j)) { alive = false; break; }
                     tc::mbar_arrive_expect_tx(&k_full[s], TILE_BYTES);
 #pragma unroll
-                    for (int h = 0; h < 2; ++h)
+                    for (int h = 0; h < HALVES; ++h)
                         tc::tma_load_3d(k_smem + s * TILE_BYTES + h * HALF_BYTES, map_k, &k_full[s], h * 64, j * BN, item.bh);
                     if (!tc::mbar_wait(&v_empty[s], ph ^ 1, guard, tc::WAIT_SMEM_EMPTY, 1000 + j)) { alive = false; break; }
                     tc::mbar_arrive_expect_tx(&v_full[s], TILE_BYTES);
 #pragma unroll
-                    for (int h = 0; h < 2; ++h)
+                    for (int h = 0; h < HALVES; ++h)
                         tc::tma_load_3d(v_smem + s * TILE_BYTES + h * HALF_BYTES, map_v, &v_full[s], h * 64, j * BN, item.bh);
                     if (j == 0) {  // Q after the first K and V: its buffer frees last (the previous item's last Q K^T)
                         if (!tc::mbar_wait(q_empty, (it & 1) ^ 1, guard, tc::WAIT_SMEM_EMPTY, 9000)) { alive = false; break; }
@@ -163,7 +173,7 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
 #pragma unroll
                         for (int i = 0; i < NQ; ++i)
 #pragma unroll
-                            for (int h = 0; h < 2; ++h)
+                            for (int h = 0; h < HALVES; ++h)
                                 tc::tma_load_3d(q_smem + i * TILE_BYTES + h * HALF_BYTES, map_q, q_full, h * 64, item.q0 + i * BM, item.bh);
                     }
                 }
@@ -235,6 +245,8 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
                     if (half == 1) {
                         tc::mma_commit(&o_done[i]);
                         if (i == NQ - 1) tc::mma_commit(&v_empty[s]);
+                    } else if (OPTIMISTIC) {
+                        tc::mma_commit(&o_half[i]);
                     }
                     return true;
                 };
@@ -279,6 +291,7 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
             const int row_base = item.row_base;
             float m_used = -__int_as_float(0x7f800000);  // -inf, in units of log2
             float l = 0.0f;
+            float carried_max = -__int_as_float(0x7f800000);  // the previous tile's row maximum (raw score), not yet in m_used
             for (int j = 0; alive && j < n_mine; ++j, ++steps) {
                 if (!tc::mbar_wait(&s_full[i], steps & 1, guard, tc::WAIT_TMEM_FULL, 3000 + j)) {
                     alive = false;
@@ -301,30 +314,46 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
                         }
                     }
                 };
-                // pass 1: the row maximum (eight independent chains, the next chunk's TMEM load in flight)
-                float mx8[8];
+                // O's row times alpha, in tensor memory (every lane of the warp takes part: the accesses are warp-wide)
+                auto rescale_o = [&](float alpha) {
+#pragma unroll 1
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t orow[32];
+                        tc::tmem_ld_32x32(o_addr + c * 32, orow);
+                        tc::tmem_ld_wait();
 #pragma unroll
-                for (int u = 0; u < 8; ++u) mx8[u] = -__int_as_float(0x7f800000);
-                tc::tmem_ld_32x32(s_addr, sr[0]);
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    tc::tmem_ld_wait();
-                    if (c + 1 < 4) tc::tmem_ld_32x32(s_addr + (c + 1) * 32, sr[(c + 1) & 1]);
-                    uint32_t(&cur)[32] = sr[c & 1];
-                    add_mask(cur, c);
-                    if (diagonal) {
-#pragma unroll
-                        for (int x = 0; x < 32; ++x)
-                            if (c * 32 + x > limit) cur[x] = 0xff800000u;
+                        for (int x = 0; x < 32; ++x) orow[x] = __float_as_uint(__uint_as_float(orow[x]) * alpha);
+                        tc::tmem_st_32x32(o_addr + c * 32, orow);
                     }
+                };
+                const bool two_pass = !OPTIMISTIC || j == 0;
+                float mx = carried_max;
+                if (two_pass) {
+                    // pass 1: the row maximum (eight independent chains, the next chunk's TMEM load in flight)
+                    float mx8[8];
 #pragma unroll
-                    for (int x = 0; x < 32; x += 4)
-                        mx8[(x / 4) & 7] = emb::max3(mx8[(x / 4) & 7], emb::max3(__uint_as_float(cur[x]), __uint_as_float(cur[x + 1]),
-                                                                                 __uint_as_float(cur[x + 2])),
-                                                     __uint_as_float(cur[x + 3]));
+                    for (int u = 0; u < 8; ++u) mx8[u] = -__int_as_float(0x7f800000);
+                    tc::tmem_ld_32x32(s_addr, sr[0]);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        tc::tmem_ld_wait();
+                        if (c + 1 < 4) tc::tmem_ld_32x32(s_addr + (c + 1) * 32, sr[(c + 1) & 1]);
+                        uint32_t(&cur)[32] = sr[c & 1];
+                        add_mask(cur, c);
+                        if (diagonal) {
+#pragma unroll
+                            for (int x = 0; x < 32; ++x)
+                                if (c * 32 + x > limit) cur[x] = 0xff800000u;
+                        }
+#pragma unroll
+                        for (int x = 0; x < 32; x += 4)
+                            mx8[(x / 4) & 7] = emb::max3(mx8[(x / 4) & 7], emb::max3(__uint_as_float(cur[x]), __uint_as_float(cur[x + 1]),
+                                                                                     __uint_as_float(cur[x + 2])),
+                                                         __uint_as_float(cur[x + 3]));
+                    }
+                    mx = fmaxf(emb::max3(mx8[0], mx8[1], mx8[2]), emb::max3(emb::max3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
                 }
-                const float mx = fmaxf(emb::max3(mx8[0], mx8[1], mx8[2]), emb::max3(emb::max3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
-                tc::tmem_ld_32x32(s_addr, sr[0]);  // pass 2 starts: chunk 0 again, in flight during the bookkeeping
+                tc::tmem_ld_32x32(s_addr, sr[0]);  // the weights' pass starts: chunk 0, in flight during the bookkeeping
                 const float m_new = fmaxf(m_used, mx * shape.scale_log2);
                 // move the reference maximum only when it grew by more than 8 (a factor 256): until then the
                 // weights are at most 2^8 and the running sum and O stay consistent with the old one
@@ -334,21 +363,14 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
                     // PV(i, j-1) completed before S(i, j) did (same issuing thread, in order); the wait orders memory
                     tc::mbar_wait(&o_done[i], (steps - 1) & 1, guard, tc::WAIT_TMEM_EMPTY, 4000 + j);
                     tc::tc_fence_after_sync();
-#pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t orow[32];
-                        tc::tmem_ld_32x32(o_addr + c * 32, orow);
-                        tc::tmem_ld_wait();
-#pragma unroll
-                        for (int x = 0; x < 32; ++x) orow[x] = __float_as_uint(__uint_as_float(orow[x]) * alpha);
-                        tc::tmem_st_32x32(o_addr + c * 32, orow);
-                    }
+                    rescale_o(alpha);
                     l *= alpha;
                 }
                 if (moved) m_used = m_new;
+                carried_max = -__int_as_float(0x7f800000);
                 // pass 2: weights 2^(s * scale - m), their sum, and P as 16-bit pairs over S's own columns
                 // (chunk c of P lands on columns 16c .. 16c+15, all of them scores already consumed)
-                const unsigned long long neg_m2 = emb::pack_f2(-m_used, -m_used);
+                unsigned long long neg_m2 = emb::pack_f2(-m_used, -m_used);
                 const unsigned long long scale2 = emb::pack_f2(shape.scale_log2, shape.scale_log2);
                 unsigned long long sum2[2] = {emb::pack_f2(0.0f, 0.0f), emb::pack_f2(0.0f, 0.0f)};
 #pragma unroll
@@ -361,6 +383,54 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
 #pragma unroll
                         for (int x = 0; x < 32; ++x)
                             if (c * 32 + x > limit) cur[x] = 0xff800000u;
+                    }
+                    if (!two_pass) {
+                        // the chunk's maximum, before any of its weights is made
+                        float part[8];
+#pragma unroll
+                        for (int x = 0; x < 32; x += 4)
+                            part[x / 4] = fmaxf(emb::max3(__uint_as_float(cur[x]), __uint_as_float(cur[x + 1]), __uint_as_float(cur[x + 2])),
+                                                __uint_as_float(cur[x + 3]));
+                        const float cm = fmaxf(emb::max3(part[0], part[1], part[2]), emb::max3(emb::max3(part[3], part[4], part[5]), part[6], part[7]));
+                        carried_max = fmaxf(carried_max, cm);
+                        const bool over = cm * shape.scale_log2 - m_used > 15.0f;  // its weight would not fit 16 bits
+                        if (__any_sync(0xffffffffu, over)) {
+                            tc::tmem_ld_wait();  // the next chunk's scores, in flight, land in their registers first
+                            const float m_now = over ? cm * shape.scale_log2 : m_used;
+                            const float alpha = over ? emb::ex2_approx_ftz(m_used - m_now) : 1.0f;
+                            // O holds the earlier tiles and, from the third chunk on, this tile's first half of P V
+                            if (c >= 2)
+                                tc::mbar_wait(&o_half[i], steps & 1, guard, tc::WAIT_TMEM_EMPTY, 4500 + j);
+                            else
+                                tc::mbar_wait(&o_done[i], (steps - 1) & 1, guard, tc::WAIT_TMEM_EMPTY, 4600 + j);
+                            tc::tc_fence_after_sync();
+                            rescale_o(alpha);
+                            // this tile's weights already written and not yet handed over
+                            for (int cc = (c >= 2 ? 2 : 0); cc < c; ++cc) {
+                                uint32_t pw[16];
+                                tc::tmem_ld_32x16(s_addr + cc * 16, pw);
+                                tc::tmem_ld_wait();
+#pragma unroll
+                                for (int x = 0; x < 16; ++x) {
+                                    float lo, hi;
+                                    unpack2<BF16>(pw[x], lo, hi);
+                                    pw[x] = pack2<BF16>(lo * alpha, hi * alpha);
+                                }
+                                asm volatile(
+                                    "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                                    "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(s_addr + cc * 16),
+                                    "r"(pw[0]), "r"(pw[1]), "r"(pw[2]), "r"(pw[3]), "r"(pw[4]), "r"(pw[5]), "r"(pw[6]), "r"(pw[7]),
+                                    "r"(pw[8]), "r"(pw[9]), "r"(pw[10]), "r"(pw[11]), "r"(pw[12]), "r"(pw[13]), "r"(pw[14]), "r"(pw[15])
+                                    : "memory");
+                            }
+                            tc::tmem_st_wait();
+                            const unsigned long long alpha2 = emb::pack_f2(alpha, alpha), zero2 = emb::pack_f2(0.0f, 0.0f);
+                            sum2[0] = emb::fma_f2(sum2[0], alpha2, zero2);
+                            sum2[1] = emb::fma_f2(sum2[1], alpha2, zero2);
+                            l *= alpha;
+                            if (over) m_used = m_now;
+                            neg_m2 = emb::pack_f2(-m_used, -m_used);
+                        }
                     }
                     uint32_t packed[16];
 #pragma unroll
@@ -407,7 +477,7 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
                 const float inv = 1.0f / l;
                 out_t* dst = static_cast<out_t*>(o_out) + (static_cast<size_t>(row_base) + q_row) * D;
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < D / 32; ++c) {
                     uint32_t orow[32];
                     tc::tmem_ld_32x32(o_addr + c * 32, orow);
                     tc::tmem_ld_wait();

@@ -41,6 +41,16 @@ template <> __device__ __forceinline__ uint32_t pack2<true>(float lo, float hi) 
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+template <bool BF16> __device__ __forceinline__ void unpack2(uint32_t v, float& lo, float& hi);
+template <> __device__ __forceinline__ void unpack2<false>(uint32_t v, float& lo, float& hi) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v));
+    lo = f.x, hi = f.y;
+}
+template <> __device__ __forceinline__ void unpack2<true>(uint32_t v, float& lo, float& hi) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
+    lo = f.x, hi = f.y;
+}
+
 struct GemmShape {
     int m, n, k;
     int splits = 1;  // K is cut into this many slabs (each a multiple of 64 when there are several); C is [splits, m, n]

@@ -30,10 +30,14 @@ from .ir import dtype_name, kind
 TARGET_SMS = 148
 GEMM_STAGES = 4
 GEMM_GROUP_M = 16
+GEMM_GROUP_M_H = 32       # row-blocks per group of the MLP's first matmul (K = d_model): its B (w1, 128 MiB) is re-read from HBM once per group; measured 16: 3388, 32: 3309, 64: 3515, 8: 3419 us per pass
 GEMM_PAIR_STAGES = 6      # CTA pairs: a stage is 32 KB per CTA
 GEMM_PAIR_GROUP_M = 8     # in 256-row tiles: the same L2 footprint as 16 row-blocks of 128
 GEMM_PAIR_MIN_TILES = 74  # CTA pairs (256 x 256 tiles) only when they give every TPC of the GPU a tile; 0 switches them off
 ATTN_POLY_PERIOD = 4  # every n-th pair of softmax weights gets its 2^x from an FMA polynomial instead of the SFU (0: none)
+# From a work item's second key tile on, no pass of its own for the row maximum (emb_attention.cuh: OPTIMISTIC). Measured SLOWER on B200
+# (1142 against 1070 us on the causal 8 x 32 x 4096 x 128 workload), so it is off unless EMMY_PTX_PREFER=onepass asks for it.
+ATTN_OPTIMISTIC = False
 
 
 def wrapper(src, includes: str, body: list, extra_sig: list, threads: int, min_blocks: int = 1, cluster: int = 1) -> str:
@@ -43,6 +47,12 @@ def wrapper(src, includes: str, body: list, extra_sig: list, threads: int, min_b
     head = [includes,
             f'extern "C" __global__ void {attrs}__launch_bounds__({threads}, {min_blocks}) {src.name}({sig}) {{']
     return "\n".join(head + codegen.pdl_prologue(src, True) + body + ["}"]) + "\n"
+
+
+def prefers(name: str) -> bool:
+    """Is the optional, not-by-default rewrite ``name`` asked for (EMMY_PTX_PREFER, a comma-separated list)?"""
+    import os
+    return name in {n.strip() for n in os.environ.get("EMMY_PTX_PREFER", "").split(",")}
 
 
 ELEMENT_BYTES = {"u8": 1, "f8e4m3": 1, "f16": 2, "bf16": 2, "f32": 4}
@@ -269,7 +279,7 @@ def _assign(stmts: dict, name, op=None):
     return st
 
 
-def match_attention(src, strict: bool) -> Plan:
+def match_attention(src, strict: bool, disable=frozenset()) -> Plan:
     """emmy's fused attention (examples/a01_attention/k_matmul_softmax_reduce_b55365.ir.txt,
     tests/test_oracle.py:204-231): per (row, output column) thread a key loop that recomputes the row's
     score, then the online update gn = max(m, s), alpha = exp(m - gn), beta = exp(s - gn),
@@ -284,7 +294,7 @@ def match_attention(src, strict: bool) -> Plan:
     lead = tile.axes[:-2]
     q_axis, c_axis = tile.axes[-2].name, tile.axes[-1].name
     S, D = tile.axes[-2].extent.as_static(), tile.axes[-1].extent.as_static()
-    need(D == 128 and src.launch.block == D, "the head dimension (= block) is not 128")
+    need(D in (64, 128) and src.launch.block == D, "the head dimension (= block) is neither 64 nor 128")
     body = list(tile.body)
     # constants named before the key loop: literal Lets, scalars loaded from ConstantOp buffers, reciprocals of those
     consts, at = {}, 0
@@ -403,7 +413,7 @@ def match_attention(src, strict: bool) -> Plan:
     bufs = [src.buffers.get(n) for n in (ql.input, kl.input, vload.input, write.output)]
     need(all(b is not None for b in bufs), "unknown buffers")
     shape = tuple(a.extent.as_static() for a in lead) + (S, D)
-    need(all(tuple(b.shape) == shape for b in bufs), "Q, K, V, O do not share the shape [.., S, 128]")
+    need(all(tuple(b.shape) == shape for b in bufs), "Q, K, V, O do not share the shape [.., S, D]")
     dt = bufs[0].dtype
     need(dt in ("f16", "bf16") and all(b.dtype == dt for b in bufs), "Q, K, V, O are not all f16 or all bf16")
     need(not ({ql.input, kl.input, vload.input} & set(src.written)), "the kernel writes an operand")
@@ -415,10 +425,11 @@ def match_attention(src, strict: bool) -> Plan:
     items = bh * math.ceil(S / (nq * 128))
     grid = min(TARGET_SMS, items)
     threads = 64 + 128 * nq
-    smem = (nq + 4) * 32768 + 1024 + 256
+    smem = (nq + 4) * (D // 64) * 16384 + 1024 + 256
     scale_log2 = scale * math.log2(math.e)
     masked = mask_load is not None
-    call = [f"    emb::attention_fwd_kernel<{nq}, {str(causal).lower()}, {str(dt == 'bf16').lower()}, {ATTN_POLY_PERIOD}, {str(masked).lower()}>("
+    onepass = (ATTN_OPTIMISTIC or prefers("onepass")) and "onepass" not in disable
+    call = [f"    emb::attention_fwd_kernel<{nq}, {str(causal).lower()}, {str(dt == 'bf16').lower()}, {ATTN_POLY_PERIOD}, {str(masked).lower()}, {str(onepass).lower()}, {D}>("
             f"&tmap_q, &tmap_k, &tmap_v, p_{write.output}, emb::AttnShape{{{bh}, {S}, {codegen.c_float(scale_log2)}, {codegen.c_float(1.0 / scale)}}}, "
             f"status{', p_' + mask_load.input if masked else ''});"]
     extra_sig = ["const __grid_constant__ CUtensorMap tmap_q", "const __grid_constant__ CUtensorMap tmap_k",
@@ -428,12 +439,14 @@ def match_attention(src, strict: bool) -> Plan:
     def head_map(name, buffer):  # (d, row of the head, head): rows past the end of a head read as zeros
         return tmap(name, buffer, dt, (D, S, bh), (D * 2, S * D * 2), (64, 128, 1))
     extra = [head_map("q", ql.input), head_map("k", kl.input), head_map("v", vload.input), dict(kind="status", name="status")]
-    remarks = [f"attention template: {bh} (batch, head) pairs x {S} queries, head dimension 128, {dt}, "
+    remarks = [f"attention template: {bh} (batch, head) pairs x {S} queries, head dimension {D}, {dt}, "
                f"{'causal' if causal else 'full'}{', additive per-key mask' if masked else ''}; {grid} persistent CTAs of {threads} threads claim "
                f"{items} work items of {nq} query tile(s) of 128 rows against 128-key tiles (scheduler + TMA producer, tcgen05.mma issuer, "
                "one softmax warp group per query tile); the next item's loads and first scores overlap the previous item's epilogue",
                "online softmax recognised (m, l, o with alpha = exp(m - max), beta = exp(s - max)); applied once per 128-key "
-               "tile in base 2, O rescaled in tensor memory only when the maximum moves by more than 2^8",
+               "tile in base 2, O rescaled in tensor memory only when the maximum moves by more than 2^8" +
+               ("; from an item's second key tile on the tile's maximum is tracked during the weights' pass (no pass of its own), a "
+                "score more than 2^15 above the reference moves it at once" if onepass else ""),
                "S = Q K^T and O += P V on tcgen05.mma with S, P and O in tensor memory; K, V in two TMA stages each; "
                "the CTAs of one (batch, head) are neighbours so that K and V are shared in L2"]
     if S % 128:
@@ -450,12 +463,6 @@ GELU_OPS = ["multiply", "multiply", "multiply", "multiply", "add", "multiply", "
 MLP_CLUSTER = 8            # CTAs per cluster of the fused MLP template
 MLP_FUSED_MAX_COLS = 256   # columns of y one CTA can hold in tensor memory beside two accumulators of a hidden chunk
 MLP_FUSED_CLUSTERS = 16    # clusters launched (128 of the 148 SMs: a cluster of 8 must sit inside one GPC)
-
-
-def prefers(name: str) -> bool:
-    """Is the optional, not-by-default rewrite ``name`` asked for (EMMY_PTX_PREFER, a comma-separated list)?"""
-    import os
-    return name in {n.strip() for n in os.environ.get("EMMY_PTX_PREFER", "").split(",")}
 
 
 def mlp_fused_refusal(T: int, D: int, Hd: int):
@@ -605,7 +612,7 @@ def match_mlp(src, strict: bool, disable=frozenset()) -> Plan:
              f'extern "C" __global__ void __launch_bounds__(192, 1) {e}__h(const __grid_constant__ CUtensorMap tmap_x, '
              "const __grid_constant__ CUtensorMap tmap_w1t, __nv_bfloat16* __restrict__ h, const float* __restrict__ scale, "
              "unsigned* __restrict__ status) {",
-             f"    emb::gemm_tn_kernel<{GEMM_STAGES}, {GEMM_GROUP_M}, true, emb::EPI_SCALE_GELU>(&tmap_x, &tmap_w1t, h, "
+             f"    emb::gemm_tn_kernel<{GEMM_STAGES}, {GEMM_GROUP_M_H}, true, emb::EPI_SCALE_GELU>(&tmap_x, &tmap_w1t, h, "
              f"emb::GemmShape{{{T}, {Hd}, {D}}}, status, scale);", "}",
              f'extern "C" __global__ void __launch_bounds__(192, 1) {e}({sig}, const __grid_constant__ CUtensorMap tmap_h, '
              "const __grid_constant__ CUtensorMap tmap_w2t, unsigned* __restrict__ status) {",

@@ -120,6 +120,19 @@ def test_attention_full_size_sampled_rows_and_cross_check():
     assert np.array_equal(got[:, :, 0, :], prob.host["v"][:, :, 0, :])
 
 
+@pytest.mark.parametrize("seq,causal,dtype", [(256, True, "f16"), (384, False, "bf16"), (200, True, "f16")])
+def test_attention_with_head_dimension_64(tmp_path, seq, causal, dtype):
+    p = problems.attention(batch=2, heads=2, seq=seq, dim=64, causal=causal, dtype=dtype, ident="t")
+    prob = runner.Problem(problems.write(p, tmp_path), "optimized", canary=True)
+    assert prob.kernels[0].launch_info["family"] == "blocking"
+    got = prob.run()["attn"]
+    prob.check_canaries()
+    blocks = ragged_rows(4, seq)
+    want = oracle_problem(p, prob.host, blocks=blocks)["attn"].reshape(-1, 64)
+    check(got.reshape(-1, 64)[blocks], want[blocks], dtype, f"D=64 S={seq} causal={causal} sampled rows vs oracle")
+    check(got, f64_attention(prob.host, causal, float(np.float32(1 / np.sqrt(64)))), dtype, f"D=64 S={seq} causal={causal} all rows vs f64")
+
+
 def f64_attention(host, causal, scale, mask=None):
     q, k, v = (host[n].astype(np.float64) for n in "qkv")
     s = np.einsum("bhqd,bhkd->bhqk", q, k) * scale
@@ -180,3 +193,27 @@ def test_attention_with_an_additive_mask_and_a_masked_tile(tmp_path, seq, causal
     check(got.reshape(-1, 128)[blocks], want[blocks], "f16", f"masked S={seq} causal={causal} sampled rows vs oracle")
     scale = float(np.float32(1.0) / np.float32(np.sqrt(128)))
     check(got, f64_attention(host, causal, scale, mask), "f16", f"masked S={seq} causal={causal} all rows vs f64")
+
+
+def test_attention_with_the_maximum_tracked_in_one_pass(tmp_path, monkeypatch):
+    """EMMY_PTX_PREFER=onepass: from the second key tile on the weights are taken against the carried reference maximum
+    while the tile's own maximum is tracked; a score more than 2^15 above the reference moves it at once (O, the running
+    sum and the tile's unconsumed weights rescaled). Ordinary scores, and scores that keep growing along the keys so
+    that both the lazy move and the at-once move happen, in the first and in the second half of a tile."""
+    monkeypatch.setenv("EMMY_PTX_PREFER", "onepass")
+    p = problems.attention(batch=1, heads=2, seq=512, dim=128, ident="t")
+    folder = problems.write(p, tmp_path)
+    prob = runner.Problem(folder, "optimized")
+    assert "true>(&tmap_q" in prob.kernels[0].ptx or prob.kernels[0].launch_info["family"] == "blocking"
+    compare_rows(p, prob, prob.run()["attn"])
+    rng = np.random.default_rng(11)
+    q = rng.standard_normal((1, 2, 512, 128)).astype(np.float16)
+    k = (rng.standard_normal((1, 2, 512, 128)) * np.linspace(0.2, 10.0, 512)[None, None, :, None]).astype(np.float16)
+    k[0, 0, 200] *= 6  # a jump in the second half of the second tile
+    k[0, 1, 300] *= 6  # ... and in the first half of the third
+    v = rng.standard_normal((1, 2, 512, 128)).astype(np.float16)
+    host = {"q": q, "k": k, "v": v}
+    prob = runner.Problem(folder, "optimized", inputs=host)
+    got = prob.run()["attn"]
+    compare_rows(p, prob, got, host=host)
+    check(got, f64_attention(host, True, float(np.float32(1 / np.sqrt(128)))), "f16", "one-pass maximum, growing scores, all rows vs f64")

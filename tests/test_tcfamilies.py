@@ -77,11 +77,14 @@ def test_attention_is_taken_and_refused(tmp_path):
     masked = load(tmp_path, problems.attention(batch=1, heads=1, seq=256, dim=128, causal=False, mask=True, scale_as="reciprocal", ident="e"),
                   "k_attention")
     plan = tcfamilies.match_attention(masked, False)
-    assert "attention_fwd_kernel<2, false, false, 4, true>" in plan.source and ", p_mask);" in plan.source
+    assert "attention_fwd_kernel<2, false, false, 4, true, false, 128>" in plan.source and ", p_mask);" in plan.source
     assert "0.12751" in plan.source and "11.3137" in plan.source  # log2(e) / sqrt(128) and sqrt(128), from the constant's value
     narrow = load(tmp_path, problems.attention(batch=1, heads=1, seq=128, dim=64, ident="d"), "k_attention")
+    plan = tcfamilies.match_attention(narrow, False)
+    assert plan.source.count(", 64>(&tmap_q") == 1 and plan.smem_bytes == 5 * 16384 + 1280
+    odd = load(tmp_path, problems.attention(batch=1, heads=1, seq=128, dim=32, ident="d32"), "k_attention")
     with pytest.raises(families.Refusal, match="head dimension"):
-        tcfamilies.match_attention(narrow, False)
+        tcfamilies.match_attention(odd, False)
     # the maximum must move LAST: an update that moves m before the sums read it is not the online softmax
     def early_max(b):
         loop = next(s for s in b if ir.kind(s) == "StridedLoop")
