@@ -69,9 +69,9 @@ def _mlp_work(k):
 
 
 WORKLOADS = {
-    # name: problem folder of the one-GPU size, what bounds the dominant kernel, its index among the pass's launches,
-    # and the algorithmic work of one launch as a function of the (shard's) sizes
-    "mlp": dict(folder="k_mlp_gelu_tanh_16384x4096x16384", bound="tensor", dominant=2, dtype="bf16", work=_mlp_work,
+    # name: problem folder of the one-GPU size, what bounds the dominant kernel, that kernel (its index among the pass's
+    # launches, or its entry), and the algorithmic work of one launch as a function of the (shard's) sizes
+    "mlp": dict(folder="k_mlp_gelu_tanh_16384x4096x16384", bound="tensor", dominant="k_mlp_gelu__h", dtype="bf16", work=_mlp_work,
                 describe="GELU MLP 16384x4096x16384, bf16 x, e4m3 weights decoded to bf16, bf16 tcgen05 MMA (BASELINE configs[4])"),
     "softmax": dict(folder="f_softmax_8192x4096", bound="hbm", dominant=0, dtype="f32", work=_rows_work,
                     describe="row softmax [8192,4096] f32 (BASELINE configs[1])"),
@@ -94,10 +94,10 @@ WORKLOADS = {
                        describe="f32 array sum of 2^24 in emmy's scalar spelling, regrouped into 16-byte chunks"),
     # a mid-size MLP whose d_model fits the cluster-fused template (EMMY_PTX_PREFER=dsmem), as the default two-matmul
     # chain and fused: the measured reason why the chain is the default
-    "mlp_2048": dict(folder="k_mlp_gelu_tanh_16384x2048x8192", bound="tensor", dominant=2, dtype="bf16", work=_mlp_work,
+    "mlp_2048": dict(folder="k_mlp_gelu_tanh_16384x2048x8192", bound="tensor", dominant="k_mlp_gelu__h", dtype="bf16", work=_mlp_work,
                      sizes=dict(tokens=16384, d_model=2048, hidden=8192),
                      describe="GELU MLP 16384x2048x8192 as decode + two tcgen05 matmuls (the default)"),
-    "mlp_2048_fused": dict(folder="k_mlp_gelu_tanh_16384x2048x8192", bound="tensor", dominant=2, dtype="bf16", prefer="dsmem",
+    "mlp_2048_fused": dict(folder="k_mlp_gelu_tanh_16384x2048x8192", bound="tensor", dominant="k_mlp_gelu", dtype="bf16", prefer="dsmem",
                            work=lambda k: dict(flops=2 * _mlp_work(k)["flops"]), sizes=dict(tokens=16384, d_model=2048, hidden=8192),
                            describe="GELU MLP 16384x2048x8192 fused in clusters of 8 (hidden chunks through distributed shared memory)"),
     # the matmul handed over as a warp-level mma.sync schedule (fragment form) plus its fold kernel: optimized mode proves
@@ -499,10 +499,11 @@ def main() -> None:
         per_launch = prob.time_rotating_us(warmup=3, iters=max(10, min(steps, 50)), batch=1)  # one event pair per pass
         # the dominant kernel alone over the same kind of timed region, for the roofline (the pass itself when it is one launch)
         entries = [(e, k) for k in prob.kernels for e in [p_["entry"] for p_ in k.launch_info.get("pre", ())] + [k.meta["entry"]]]
+        dominant = w["dominant"] if isinstance(w["dominant"], int) else [e for e, _ in entries].index(w["dominant"])
         if len(prob.launches) == 1 and not nccl:
             dom_us = mean_us
         else:
-            dom_us = all_max(prob.time_rotating_us(warmup=warmup, iters=1, batch=steps, only=w["dominant"])[0])
+            dom_us = all_max(prob.time_rotating_us(warmup=warmup, iters=1, batch=steps, only=dominant)[0])
         if w["bound"] == "hbm":
             achieved = work["bytes"] / dom_us / 1e3  # GB/s
             peak, unit = float(pk["hbm_gbs"]), "GB/s"
@@ -513,7 +514,7 @@ def main() -> None:
             long_run = steps * mean_us > 1e6 and "bf16_tflops_sustained" in pk
             peak, unit = float(pk["bf16_tflops_sustained" if long_run else "bf16_tflops"]), "TFLOP/s"
             whole = work.get("chain_flops", work["flops"]) * 1.0
-        dom_entry, dom_kernel = entries[w["dominant"]]
+        dom_entry, dom_kernel = entries[dominant]
         traffic = NCU_TRAFFIC.get(workload)
         roof = dict(bound=w["bound"], achieved=achieved, peak=peak, unit=unit, frac=achieved / peak,
                     traffic=traffic if world == 1 else None, kernel=dom_entry, kernel_us=dom_us,

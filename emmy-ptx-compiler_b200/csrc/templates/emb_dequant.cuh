@@ -11,6 +11,10 @@ namespace emb {
 
 // 64 x 64 tile per CTA of 256 threads, through shared memory: 16-byte global reads along C, 16-byte global
 // writes along R.
+// WAIT_PRIOR: the kernel is launched programmatically dependent on the kernel before it in the stream, whose data it does
+// not need: it runs beside that kernel, and ONE thread waits for it at the very end, so that this grid - and with it
+// whatever the stream holds next - completes only after that kernel has.
+template <bool WAIT_PRIOR = false>
 __device__ __forceinline__ void dequant_transpose_e4m3(const uint8_t* __restrict__ codes, __nv_bfloat16* __restrict__ out, int rows,
                                                        int cols) {
     __shared__ __nv_bfloat16 tile[64][64 + 8];
@@ -55,6 +59,7 @@ __device__ __forceinline__ void dequant_transpose_e4m3(const uint8_t* __restrict
             }
         }
     }
+    if (WAIT_PRIOR && blockIdx.x == 0 && threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 }  // namespace emb

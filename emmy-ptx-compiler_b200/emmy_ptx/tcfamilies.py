@@ -608,26 +608,36 @@ def match_mlp(src, strict: bool, disable=frozenset()) -> Plan:
     smem = GEMM_STAGES * stage + 1024 + 256
     tiles1 = math.ceil(T / 128) * math.ceil(Hd / 256)
     tiles2 = math.ceil(T / 128) * math.ceil(D / 256)
-    lines = ['#include "emb_gemm.cuh"', *decode,
+    # launch order: decode w1, h = gelu(x w1), decode w2, y = h w2. The second decode does not need h: it is launched
+    # programmatically dependent on the first matmul (which lets its dependents go at once), runs beside it on the SMs'
+    # spare shared memory and threads, and one of its threads waits for the matmul at the very end, so the second matmul,
+    # an ordinary launch behind it, still starts only when both are complete.
+    lines = ['#include "emb_gemm.cuh"', decode[0], *decode[1:4],
+             f'extern "C" __global__ void __launch_bounds__(256) {e}__w2(const unsigned char* __restrict__ codes, __nv_bfloat16* __restrict__ out) {{',
+             f"    emb::dequant_transpose_e4m3<true>(codes, out, {Hd}, {D});", "}",
              f'extern "C" __global__ void __launch_bounds__(192, 1) {e}__h(const __grid_constant__ CUtensorMap tmap_x, '
              "const __grid_constant__ CUtensorMap tmap_w1t, __nv_bfloat16* __restrict__ h, const float* __restrict__ scale, "
              "unsigned* __restrict__ status) {",
+             '    asm volatile("griddepcontrol.launch_dependents;");',
              f"    emb::gemm_tn_kernel<{GEMM_STAGES}, {GEMM_GROUP_M_H}, true, emb::EPI_SCALE_GELU>(&tmap_x, &tmap_w1t, h, "
              f"emb::GemmShape{{{T}, {Hd}, {D}}}, status, scale);", "}",
              f'extern "C" __global__ void __launch_bounds__(192, 1) {e}({sig}, const __grid_constant__ CUtensorMap tmap_h, '
              "const __grid_constant__ CUtensorMap tmap_w2t, unsigned* __restrict__ status) {",
              f"    emb::gemm_tn_kernel<{GEMM_STAGES}, {GEMM_GROUP_M}, true, emb::EPI_SCALE>(&tmap_h, &tmap_w2t, p_{w.output}, "
              f"emb::GemmShape{{{T}, {D}, {Hd}}}, status, p_{s2_buf});", "}"]
-    pre.append(
-        dict(entry=f"{e}__h", grid=[min(TARGET_SMS, tiles1), 1, 1], block=[192, 1, 1], cluster=1, smem_bytes=smem,
-             params=[tmap("x", lx.input, "bf16", (D, T), (D * 2,), (64, 128)), tmap("w1t", "w1t", "bf16", (D, Hd), (D * 2,), (64, 256)),
-                     dict(kind="scratch", name="h", bytes=T * Hd * 2), dict(kind="buffer", name=s1_buf), dict(kind="status", name="status")]))
+    w2_decode = dict(pre[1], pdl=True)
+    pre = [pre[0],
+           dict(entry=f"{e}__h", grid=[min(TARGET_SMS, tiles1), 1, 1], block=[192, 1, 1], cluster=1, smem_bytes=smem,
+                params=[tmap("x", lx.input, "bf16", (D, T), (D * 2,), (64, 128)), tmap("w1t", "w1t", "bf16", (D, Hd), (D * 2,), (64, 256)),
+                        dict(kind="scratch", name="h", bytes=T * Hd * 2), dict(kind="buffer", name=s1_buf), dict(kind="status", name="status")]),
+           w2_decode]
     extra = [tmap("h", "h", "bf16", (Hd, T), (Hd * 2,), (64, 128)), tmap("w2t", "w2t", "bf16", (Hd, D), (Hd * 2,), (64, 256)),
              dict(kind="status", name="status")]
     remarks = [f"MLP template: {T} tokens, d_model {D}, hidden {Hd}; the e4m3 weights are decoded once to bf16 (exactly) and "
                "transposed to K-major, then two tcgen05 matmuls: h = gelu_tanh(s1 x w1) with the activation in the first one's "
                "epilogue (h kept in bf16), y = s2 h w2",
-               f"four launches from one module: {e}__w1, {e}__w2 (decode), {e}__h ({tiles1} tiles), {e} ({tiles2} tiles); "
+               f"four launches from one module: {e}__w1 (decode), {e}__h ({tiles1} tiles), {e}__w2 (decode, beside {e}__h: launched "
+               f"programmatically dependent on it, waits for it only at its end), {e} ({tiles2} tiles); "
                f"scratch: {(2 * Hd * D * 2 + T * Hd * 2) >> 20} MiB",
                f"not fused in a cluster: {fused_why}; h makes one bf16 round trip through L2 / HBM between the two matmuls"]
     return Plan("clusters", "\n".join(lines) + "\n", remarks, grid=min(TARGET_SMS, tiles2), block=192, smem_bytes=smem,

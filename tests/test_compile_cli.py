@@ -149,3 +149,20 @@ def test_one_wave_hint_and_cluster_request_are_in_the_module(tmp_path):
     assert "one wave" not in report
     ptx, report = compile_(problems_dir / "m_f16_8192" / "k_matmul.ir.json")
     assert ".reqnctapercluster 2, 1, 1" in ptx and ".reqnctapercluster 2" in report
+
+
+def test_the_reference_arm_of_the_bench_runs_on_the_host_alone(tmp_path):
+    """`bench.py --impl reference` times the CPU interpreter (the oracle port) on a bounded sample and prints one JSON line
+    with the contract's keys; it needs no GPU. The array sum keeps the sample small."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    r = subprocess.run([sys.executable, str(root / "bench.py"), "--impl", "reference", "--workload", "sum", "--steps", "1"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["unit"] == "us" and line["higher_is_better"] is False and line["value"] > 0
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1 and "CTAs" in line["cpu_baseline"]["sample"]
+    assert line["e2e"] == dict(value=line["value"], unit="us", h2d_bytes_per_step=0, d2h_bytes_per_step=0)

@@ -98,7 +98,8 @@ def test_attention_is_taken_and_refused(tmp_path):
 def test_mlp_is_taken_with_its_chain_and_refused(tmp_path):
     src = load(tmp_path, problems.gelu_mlp(tokens=128, d_model=256, hidden=512, lanes=8, block=64, ident="k"), "k_mlp_gelu")
     plan = tcfamilies.match_mlp(src, False)
-    assert plan.family == "clusters" and [p["entry"] for p in plan.pre] == ["k_mlp_gelu__w1", "k_mlp_gelu__w2", "k_mlp_gelu__h"]
+    assert plan.family == "clusters" and [p["entry"] for p in plan.pre] == ["k_mlp_gelu__w1", "k_mlp_gelu__h", "k_mlp_gelu__w2"]
+    assert [bool(p.get("pdl")) for p in plan.pre] == [False, False, True] and "griddepcontrol.launch_dependents" in plan.source
     scratch = {p["name"]: p["bytes"] for pre in plan.pre for p in pre["params"] if p["kind"] == "scratch"}
     assert scratch == {"w1t": 512 * 256 * 2, "w2t": 256 * 512 * 2, "h": 128 * 512 * 2}
     with pytest.raises(families.Refusal, match="own order"):
