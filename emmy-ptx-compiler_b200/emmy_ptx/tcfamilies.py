@@ -34,10 +34,22 @@ GEMM_GROUP_M_H = 32       # row-blocks per group of the MLP's first matmul (K = 
 GEMM_PAIR_STAGES = 6      # CTA pairs: a stage is 32 KB per CTA
 GEMM_PAIR_GROUP_M = 8     # in 256-row tiles: the same L2 footprint as 16 row-blocks of 128
 GEMM_PAIR_MIN_TILES = 74  # CTA pairs (256 x 256 tiles) only when they give every TPC of the GPU a tile; 0 switches them off
-ATTN_POLY_PERIOD = 4  # every n-th pair of softmax weights gets its 2^x from an FMA polynomial instead of the SFU (0: none)
+ATTN_POLY_PERIOD = 4  # 128-key template: every n-th pair of softmax weights gets its 2^x from an FMA polynomial instead of the SFU (0: none)
 # From a work item's second key tile on, no pass of its own for the row maximum (emb_attention.cuh: OPTIMISTIC). Measured SLOWER on B200
 # (1142 against 1070 us on the causal 8 x 32 x 4096 x 128 workload), so it is off unless EMMY_PTX_PREFER=onepass asks for it.
 ATTN_OPTIMISTIC = False
+# Key tile of the attention template: 64 (two score buffers per query tile and one MMA issuer per query tile, so the next scores are
+# ready before the softmax of the current ones ends, emb_attention64.cuh) or 128 (one score buffer per query tile,
+# emb_attention.cuh). Measured on the causal 8 x 32 x 4096 x 128 workload: 64: 995-1010 us, 128: 1065 us per pass.
+# EMMY_PTX_PREFER=keys64 / keys128 overrides.
+ATTN_KEY_TILE = 64
+# The 64-key template's share of polynomial exponentials: none. Its softmax warps are bound by issue slots about as much as by
+# the SFU (measured 0: 1006, 8: 1011, 4: 1011, 2: 1096 us), so trading one for the other gains nothing.
+ATTN_POLY_PERIOD_64 = 0
+# Threads per query row of the 64-key template: 1 keeps one softmax warp group per query tile; 2 puts two on it (32 scores of a
+# row each, maxima exchanged through shared memory). Measured SLOWER (1090 against 998 us): the exchange costs more than the
+# shorter per-tile chain saves, so 2 is only taken when EMMY_PTX_PREFER=split2 asks for it.
+ATTN_ROW_SPLIT = 1
 
 
 def wrapper(src, includes: str, body: list, extra_sig: list, threads: int, min_blocks: int = 1, cluster: int = 1) -> str:
@@ -425,29 +437,46 @@ def match_attention(src, strict: bool, disable=frozenset()) -> Plan:
     items = bh * math.ceil(S / (nq * 128))
     grid = min(TARGET_SMS, items)
     threads = 64 + 128 * nq
-    smem = (nq + 4) * (D // 64) * 16384 + 1024 + 256
     scale_log2 = scale * math.log2(math.e)
     masked = mask_load is not None
     onepass = (ATTN_OPTIMISTIC or prefers("onepass")) and "onepass" not in disable
-    call = [f"    emb::attention_fwd_kernel<{nq}, {str(causal).lower()}, {str(dt == 'bf16').lower()}, {ATTN_POLY_PERIOD}, {str(masked).lower()}, {str(onepass).lower()}, {D}>("
-            f"&tmap_q, &tmap_k, &tmap_v, p_{write.output}, emb::AttnShape{{{bh}, {S}, {codegen.c_float(scale_log2)}, {codegen.c_float(1.0 / scale)}}}, "
-            f"status{', p_' + mask_load.input if masked else ''});"]
+    key_tile = 64 if prefers("keys64") else 128 if prefers("keys128") or onepass else ATTN_KEY_TILE  # (one-pass exists on 128-key tiles only)
+    shape_arg = f"emb::AttnShape{{{bh}, {S}, {codegen.c_float(scale_log2)}, {codegen.c_float(1.0 / scale)}}}"
+    mask_arg = ", p_" + mask_load.input if masked else ""
+    poly = ATTN_POLY_PERIOD_64 if key_tile == 64 else ATTN_POLY_PERIOD
+    flags = f"{nq}, {str(causal).lower()}, {str(dt == 'bf16').lower()}, {poly}, {str(masked).lower()}"
+    split = 1
+    if key_tile == 64:
+        split = 1 if prefers("split1") else 2 if prefers("split2") else ATTN_ROW_SPLIT
+        threads = 32 * (1 + nq) + 128 * nq * split  # producer, one issuer per query tile, the softmax warp groups
+        smem = nq * (D // 64) * 16384 + 2 * 4 * (D // 64) * 8192 + 1024 + 512 + (4096 if split == 2 else 0)
+        include = '#include "emb_attention64.cuh"'
+        call = [f"    emb::attention_fwd_kernel64<{flags}, {D}, {split}>(&tmap_q, &tmap_k, &tmap_v, p_{write.output}, {shape_arg}, status{mask_arg});"]
+    else:
+        smem = (nq + 4) * (D // 64) * 16384 + 1024 + 256
+        include = '#include "emb_attention.cuh"'
+        call = [f"    emb::attention_fwd_kernel<{flags}, {str(onepass).lower()}, {D}>(&tmap_q, &tmap_k, &tmap_v, p_{write.output}, {shape_arg}, "
+                f"status{mask_arg});"]
     extra_sig = ["const __grid_constant__ CUtensorMap tmap_q", "const __grid_constant__ CUtensorMap tmap_k",
                  "const __grid_constant__ CUtensorMap tmap_v", "unsigned* __restrict__ status"]
-    source = wrapper(src, '#include "emb_attention.cuh"', call, extra_sig, threads)
+    source = wrapper(src, include, call, extra_sig, threads)
 
-    def head_map(name, buffer):  # (d, row of the head, head): rows past the end of a head read as zeros
-        return tmap(name, buffer, dt, (D, S, bh), (D * 2, S * D * 2), (64, 128, 1))
-    extra = [head_map("q", ql.input), head_map("k", kl.input), head_map("v", vload.input), dict(kind="status", name="status")]
+    def head_map(name, buffer, rows):  # (d, row of the head, head): rows past the end of a head read as zeros
+        return tmap(name, buffer, dt, (D, S, bh), (D * 2, S * D * 2), (64, rows, 1))
+    extra = [head_map("q", ql.input, 128), head_map("k", kl.input, key_tile), head_map("v", vload.input, key_tile),
+             dict(kind="status", name="status")]
     remarks = [f"attention template: {bh} (batch, head) pairs x {S} queries, head dimension {D}, {dt}, "
                f"{'causal' if causal else 'full'}{', additive per-key mask' if masked else ''}; {grid} persistent CTAs of {threads} threads claim "
-               f"{items} work items of {nq} query tile(s) of 128 rows against 128-key tiles (scheduler + TMA producer, tcgen05.mma issuer, "
-               "one softmax warp group per query tile); the next item's loads and first scores overlap the previous item's epilogue",
-               "online softmax recognised (m, l, o with alpha = exp(m - max), beta = exp(s - max)); applied once per 128-key "
+               f"{items} work items of {nq} query tile(s) of 128 rows against {key_tile}-key tiles (scheduler + TMA producer, "
+               f"{'one tcgen05.mma issuer per query tile' if key_tile == 64 else 'tcgen05.mma issuer'}, "
+               f"{'two softmax warp groups' if split == 2 else 'one softmax warp group'} per query tile); the next item's loads and first scores overlap the previous item's epilogue",
+               f"online softmax recognised (m, l, o with alpha = exp(m - max), beta = exp(s - max)); applied once per {key_tile}-key "
                "tile in base 2, O rescaled in tensor memory only when the maximum moves by more than 2^8" +
                ("; from an item's second key tile on the tile's maximum is tracked during the weights' pass (no pass of its own), a "
                 "score more than 2^15 above the reference moves it at once" if onepass else ""),
-               "S = Q K^T and O += P V on tcgen05.mma with S, P and O in tensor memory; K, V in two TMA stages each; "
+               "S = Q K^T and O += P V on tcgen05.mma with S, P and O in tensor memory; K, V in " +
+               ("four TMA stages each, the scores double-buffered so that the next tile's are ready before the current softmax ends; "
+                if key_tile == 64 else "two TMA stages each; ") +
                "the CTAs of one (batch, head) are neighbours so that K and V are shared in L2"]
     if S % 128:
         remarks.append(f"{S} keys are not a multiple of the 128-key tile: the last tile's slots past the end score -inf, its rows "

@@ -217,3 +217,30 @@ def test_attention_with_the_maximum_tracked_in_one_pass(tmp_path, monkeypatch):
     got = prob.run()["attn"]
     compare_rows(p, prob, got, host=host)
     check(got, f64_attention(host, True, float(np.float32(1 / np.sqrt(128)))), "f16", "one-pass maximum, growing scores, all rows vs f64")
+
+
+@pytest.mark.parametrize("form,marker", [("keys128", "attention_fwd_kernel<"), ("keys64,split2", ", 2>(&tmap_q")])
+@pytest.mark.parametrize("seq,dim,causal,dtype,mask", [(512, 128, True, "f16", False), (384, 128, False, "bf16", False),
+                                                      (300, 128, True, "f16", True), (200, 64, True, "f16", False),
+                                                      (129, 128, False, "f16", False)])
+def test_attention_in_its_other_forms(tmp_path, monkeypatch, form, marker, seq, dim, causal, dtype, mask):
+    """The forms that are not the default one (EMMY_PTX_PREFER): 128-key tiles with one score buffer per query tile, and the
+    64-key template with two threads per query row. Same shapes, edges and tolerances as the default form's tests: whole
+    and ragged tiles, both head dimensions, an additive mask, both 16-bit types; twice, so that a second launch finds
+    every barrier and the tensor memory as a first one does."""
+    from emmy_ptx import frontend, tcfamilies
+    monkeypatch.setenv("EMMY_PTX_PREFER", form)
+    p = problems.attention(batch=1, heads=3, seq=seq, dim=dim, causal=causal, dtype=dtype, mask=mask, ident="t")
+    folder = problems.write(p, tmp_path)
+    assert marker in tcfamilies.match_attention(frontend.load(folder / "k_attention.ir.json"), False).source
+    prob = runner.Problem(folder, "optimized", canary=True)
+    assert prob.kernels[0].launch_info["family"] == "blocking"
+    scale = float(np.float32(1 / np.sqrt(dim)))
+    want = f64_attention(prob.host, causal, scale, prob.host["mask"] if mask else None)
+    blocks = ragged_rows(3, seq)
+    rows = oracle_problem(p, prob.host, blocks=blocks)["attn"].reshape(-1, dim)
+    for _ in range(2):
+        got = prob.run()["attn"]
+        prob.check_canaries()
+        check(got.reshape(-1, dim)[blocks], rows[blocks], dtype, f"{form} S={seq} D={dim} sampled rows vs oracle")
+        check(got, want, dtype, f"{form} S={seq} D={dim} all rows vs f64")

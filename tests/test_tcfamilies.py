@@ -58,30 +58,48 @@ def test_matmul_refusals(tmp_path):
         tcfamilies.match_matmul(odd, False)
 
 
-def test_attention_is_taken_and_refused(tmp_path):
+def test_attention_is_taken_and_refused(tmp_path, monkeypatch):
+    monkeypatch.delenv("EMMY_PTX_PREFER", raising=False)
     src = load(tmp_path, problems.attention(batch=1, heads=2, seq=256, dim=128, ident="a"), "k_attention")
     plan = tcfamilies.match_attention(src, False)
-    assert plan.family == "blocking" and plan.grid == 2 and plan.block == 320 and "attention_fwd_kernel<2, true, false" in plan.source
+    # the default form: 64-key tiles, a producer warp, one issuer warp per query tile, one softmax warp group per query tile
+    assert plan.family == "blocking" and plan.grid == 2 and plan.block == 32 * 3 + 256
+    assert "attention_fwd_kernel64<2, true, false, 0, false, 128, 1>" in plan.source
+    assert plan.smem_bytes == 2 * 32768 + 2 * 4 * 16384 + 1024 + 512
     full = load(tmp_path, problems.attention(batch=1, heads=1, seq=128, dim=128, causal=False, ident="b"), "k_attention")
     plan = tcfamilies.match_attention(full, False)
-    assert plan.block == 192 and "attention_fwd_kernel<1, false, false" in plan.source
+    assert plan.block == 32 * 2 + 128 and "attention_fwd_kernel64<1, false, false" in plan.source
     with pytest.raises(families.Refusal, match="own order"):
         tcfamilies.match_attention(src, True)
     # any key count is taken: a partial last tile, rows past the end read as zeros through three-dimensional tensor maps
     short = load(tmp_path, problems.attention(batch=1, heads=3, seq=96, dim=128, ident="c"), "k_attention")
     plan = tcfamilies.match_attention(short, False)
-    assert "attention_fwd_kernel<1, true, false" in plan.source and any("not a multiple of the 128-key tile" in r for r in plan.remarks)
-    maps = [q for q in plan.extra_params if q["kind"] == "tmap"]
-    assert all(q["dims"] == [128, 96, 3] and q["box"] == [64, 128, 1] and q["strides_bytes"] == [256, 96 * 256] for q in maps)
+    assert "attention_fwd_kernel64<1, true, false" in plan.source and any("not a multiple of the 128-key tile" in r for r in plan.remarks)
+    maps = {q["name"]: q for q in plan.extra_params if q["kind"] == "tmap"}
+    assert all(q["dims"] == [128, 96, 3] and q["strides_bytes"] == [256, 96 * 256] for q in maps.values())
+    assert maps["q"]["box"] == [64, 128, 1] and maps["k"]["box"] == maps["v"]["box"] == [64, 64, 1]
     # an additive per-key mask and the scale as the reciprocal of a division's constant
     masked = load(tmp_path, problems.attention(batch=1, heads=1, seq=256, dim=128, causal=False, mask=True, scale_as="reciprocal", ident="e"),
                   "k_attention")
     plan = tcfamilies.match_attention(masked, False)
-    assert "attention_fwd_kernel<2, false, false, 4, true, false, 128>" in plan.source and ", p_mask);" in plan.source
+    assert "attention_fwd_kernel64<2, false, false, 0, true, 128, 1>" in plan.source and ", p_mask);" in plan.source
     assert "0.12751" in plan.source and "11.3137" in plan.source  # log2(e) / sqrt(128) and sqrt(128), from the constant's value
     narrow = load(tmp_path, problems.attention(batch=1, heads=1, seq=128, dim=64, ident="d"), "k_attention")
     plan = tcfamilies.match_attention(narrow, False)
-    assert plan.source.count(", 64>(&tmap_q") == 1 and plan.smem_bytes == 5 * 16384 + 1280
+    assert plan.source.count(", 64, 1>(&tmap_q") == 1 and plan.smem_bytes == 16384 + 2 * 4 * 8192 + 1024 + 512
+    # the other forms, on request: 128-key tiles (one score buffer per query tile, one issuer); two threads per query row
+    monkeypatch.setenv("EMMY_PTX_PREFER", "keys128")
+    plan = tcfamilies.match_attention(src, False)
+    assert plan.block == 320 and "attention_fwd_kernel<2, true, false, 4, false, false, 128>" in plan.source
+    assert all(q["box"] == [64, 128, 1] for q in plan.extra_params if q["kind"] == "tmap")
+    assert tcfamilies.match_attention(narrow, False).smem_bytes == 5 * 16384 + 1280
+    monkeypatch.setenv("EMMY_PTX_PREFER", "onepass")  # the one-pass maximum exists on 128-key tiles only
+    assert "attention_fwd_kernel<2, true, false, 4, false, true, 128>" in tcfamilies.match_attention(src, False).source
+    monkeypatch.setenv("EMMY_PTX_PREFER", "split2")
+    plan = tcfamilies.match_attention(src, False)
+    assert plan.block == 32 * 3 + 512 and "attention_fwd_kernel64<2, true, false, 0, false, 128, 2>" in plan.source
+    assert plan.smem_bytes == 2 * 32768 + 2 * 4 * 16384 + 1024 + 512 + 4096
+    monkeypatch.delenv("EMMY_PTX_PREFER")
     odd = load(tmp_path, problems.attention(batch=1, heads=1, seq=128, dim=32, ident="d32"), "k_attention")
     with pytest.raises(families.Refusal, match="head dimension"):
         tcfamilies.match_attention(odd, False)
