@@ -167,6 +167,26 @@ def test_attention_with_a_partial_last_tile(tmp_path, seq, causal):
     check(got, f64_attention(prob.host, causal, float(np.float32(1 / np.sqrt(128)))), "f16", f"ragged S={seq} causal={causal} all rows vs f64")
 
 
+def test_attention_with_a_long_ragged_head(tmp_path):
+    """4096 - 64 keys: 31 whole query blocks of 128 rows and a last one of 64, work items of one query tile each (the count
+    is no multiple of 256), 63 key tiles of 64; sampled rows against the oracle, every row against float64."""
+    seq = 4096 - 64
+    p = problems.attention(batch=1, heads=2, seq=seq, dim=128, causal=True, ident="t")
+    prob = runner.Problem(problems.write(p, tmp_path), "optimized", canary=True)
+    assert prob.kernels[0].launch_info["family"] == "blocking"
+    got = prob.run()["attn"]
+    prob.check_canaries()
+    blocks = ragged_rows(2, seq)
+    want = oracle_problem(p, prob.host, blocks=blocks)["attn"].reshape(-1, 128)
+    check(got.reshape(-1, 128)[blocks], want[blocks], "f16", f"ragged S={seq} sampled rows vs oracle")
+    ref = np.concatenate([f64_attention({n: prob.host[n][:, h:h + 1] for n in "qkv"}, True, float(np.float32(1 / np.sqrt(128))))
+                          for h in range(2)], axis=1)
+    stated_margin(got.astype(np.float64), ref, RTOL, f"attention f16 ragged S={seq} all rows vs f64")
+    rtol = RTOL + ULP["f16"]
+    atol = rtol * np.sqrt(np.mean(ref ** 2, axis=-1, keepdims=True))
+    assert float(np.max(np.abs(got - ref) / (atol + rtol * np.abs(ref)))) <= 1
+
+
 @pytest.mark.parametrize("seq,causal", [(256, False), (300, False), (384, True)])
 def test_attention_with_an_additive_mask_and_a_masked_tile(tmp_path, seq, causal):
     """The reference's blocked-attention test (tests/test_gpu_lowering.py:256-306: softmax(q k^T * scale + mask) v with
