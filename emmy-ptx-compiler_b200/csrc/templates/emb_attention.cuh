@@ -39,6 +39,7 @@ struct AttnShape {
                        // (as the reference fills the slots past the end of its last key block, emmy_ptx/mapping.py:743-754)
     float scale_log2;  // softmax scale * log2(e)
     float inv_scale;   // 1 / softmax scale (used with a mask only)
+    int longest_first; // work items ordered by length over all heads (else head by head)
 };
 
 // The tensor maps are three-dimensional, (d, row of the head, head): rows past the end of a head read as zeros,
@@ -101,7 +102,10 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
     };
     auto decode = [&](int w) {
         Item it;
-        const int bh = w / q_blocks, qb = q_blocks - 1 - (w % q_blocks);
+        // work-item order: the blocks of one head together, longest first (its K and V stay in L2 while its blocks run), or,
+        // when every head's K and V fit L2 at once, the longest blocks of ALL heads first (a better balanced end of the launch)
+        const int bh = shape.longest_first ? w % shape.batch_heads : w / q_blocks;
+        const int qb = q_blocks - 1 - (shape.longest_first ? w / shape.batch_heads : w % q_blocks);
         it.q0 = qb * NQ * BM;
         it.bh = bh;
         it.row_base = bh * shape.seq;

@@ -89,7 +89,10 @@ __device__ __forceinline__ void attention_fwd_kernel64(const CUtensorMap* __rest
     };
     auto decode = [&](int w) {
         Item it;
-        const int bh = w / q_blocks, qb = q_blocks - 1 - (w % q_blocks);
+        // work-item order: the blocks of one head together, longest first (its K and V stay in L2 while its blocks run), or,
+        // when every head's K and V fit L2 at once, the longest blocks of ALL heads first (a better balanced end of the launch)
+        const int bh = shape.longest_first ? w % shape.batch_heads : w / q_blocks;
+        const int qb = q_blocks - 1 - (shape.longest_first ? w / shape.batch_heads : w % q_blocks);
         it.q0 = qb * NQ * BM;
         it.bh = bh;
         it.row_base = bh * shape.seq;
