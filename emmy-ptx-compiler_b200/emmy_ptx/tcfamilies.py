@@ -596,15 +596,18 @@ def match_mlp(src, strict: bool, disable=frozenset()) -> Plan:
     e = src.name
     s1_buf, s2_buf = scalars[s1[0]], scalars[s2[0]]
     sig = codegen.signature(src)
+    def decode_grid(rows, cols, stream):  # CTAs of the decode: 64 x 128 tiles on the streaming path, else 64 x 64
+        return (rows // 64) * (cols // 128) if stream else math.ceil(rows / 64) * math.ceil(cols / 64)
+    stream1, stream2 = D % 64 == 0 and Hd % 128 == 0, Hd % 64 == 0 and D % 128 == 0
     decode = ['#include "emb_dequant.cuh"',
               f'extern "C" __global__ void __launch_bounds__(256) {e}__w1(const unsigned char* __restrict__ codes, __nv_bfloat16* __restrict__ out) {{',
-              f"    emb::dequant_transpose_e4m3(codes, out, {D}, {Hd});", "}",
+              f"    emb::dequant_transpose_e4m3<false, {str(stream1).lower()}>(codes, out, {D}, {Hd});", "}",
               f'extern "C" __global__ void __launch_bounds__(256) {e}__w2(const unsigned char* __restrict__ codes, __nv_bfloat16* __restrict__ out) {{',
-              f"    emb::dequant_transpose_e4m3(codes, out, {Hd}, {D});", "}"]
+              f"    emb::dequant_transpose_e4m3<false, {str(stream2).lower()}>(codes, out, {Hd}, {D});", "}"]
     pre = [
-        dict(entry=f"{e}__w1", grid=[math.ceil(D / 64) * math.ceil(Hd / 64), 1, 1], block=[256, 1, 1], cluster=1, smem_bytes=0,
+        dict(entry=f"{e}__w1", grid=[decode_grid(D, Hd, stream1), 1, 1], block=[256, 1, 1], cluster=1, smem_bytes=0,
              params=[dict(kind="buffer", name=lw.input), dict(kind="scratch", name="w1t", bytes=Hd * D * 2)]),
-        dict(entry=f"{e}__w2", grid=[math.ceil(Hd / 64) * math.ceil(D / 64), 1, 1], block=[256, 1, 1], cluster=1, smem_bytes=0,
+        dict(entry=f"{e}__w2", grid=[decode_grid(Hd, D, stream2), 1, 1], block=[256, 1, 1], cluster=1, smem_bytes=0,
              params=[dict(kind="buffer", name=lw2.input), dict(kind="scratch", name="w2t", bytes=D * Hd * 2)]),
     ]
     if "dsmem" in disable:
@@ -650,7 +653,7 @@ def match_mlp(src, strict: bool, disable=frozenset()) -> Plan:
     # an ordinary launch behind it, still starts only when both are complete.
     lines = ['#include "emb_gemm.cuh"', decode[0], *decode[1:4],
              f'extern "C" __global__ void __launch_bounds__(256) {e}__w2(const unsigned char* __restrict__ codes, __nv_bfloat16* __restrict__ out) {{',
-             f"    emb::dequant_transpose_e4m3<true>(codes, out, {Hd}, {D});", "}",
+             f"    emb::dequant_transpose_e4m3<true, false>(codes, out, {Hd}, {D});", "}",
              f'extern "C" __global__ void __launch_bounds__(192, 1) {e}__h(const __grid_constant__ CUtensorMap tmap_x, '
              "const __grid_constant__ CUtensorMap tmap_w1t, __nv_bfloat16* __restrict__ h, const float* __restrict__ scale, "
              "unsigned* __restrict__ status) {",
@@ -661,7 +664,7 @@ def match_mlp(src, strict: bool, disable=frozenset()) -> Plan:
              "const __grid_constant__ CUtensorMap tmap_w2t, unsigned* __restrict__ status) {",
              f"    emb::gemm_tn_kernel<{GEMM_STAGES}, {GEMM_GROUP_M}, true, emb::EPI_SCALE>(&tmap_h, &tmap_w2t, p_{w.output}, "
              f"emb::GemmShape{{{T}, {D}, {Hd}}}, status, p_{s2_buf});", "}"]
-    w2_decode = dict(pre[1], pdl=True)
+    w2_decode = dict(pre[1], pdl=True, grid=[decode_grid(Hd, D, False), 1, 1])  # (beside the matmul: the general path, see emb_dequant.cuh)
     pre = [pre[0],
            dict(entry=f"{e}__h", grid=[min(TARGET_SMS, tiles1), 1, 1], block=[192, 1, 1], cluster=1, smem_bytes=smem,
                 params=[tmap("x", lx.input, "bf16", (D, T), (D * 2,), (64, 128)), tmap("w1t", "w1t", "bf16", (D, Hd), (D * 2,), (64, 256)),
