@@ -100,6 +100,13 @@ def test_attention_is_taken_and_refused(tmp_path, monkeypatch):
     assert plan.block == 32 * 3 + 512 and "attention_fwd_kernel64<2, true, false, 0, false, 128, 2>" in plan.source
     assert plan.smem_bytes == 2 * 32768 + 2 * 4 * 16384 + 1024 + 512 + 4096
     monkeypatch.delenv("EMMY_PTX_PREFER")
+    # work-item order: longest first over all heads while every head's K and V fit L2 together, else head by head
+    assert "f, 1}, status" in tcfamilies.match_attention(src, False).source
+    big = load(tmp_path, problems.attention(batch=8, heads=32, seq=4096, dim=128, ident="big"), "k_attention")
+    assert "f, 0}, status" in tcfamilies.match_attention(big, False).source
+    shard = load(tmp_path, problems.attention(batch=1, heads=32, seq=4096, dim=128, ident="shard"), "k_attention")
+    assert "f, 1}, status" in tcfamilies.match_attention(shard, False).source
+    assert "f, 0}, status" in tcfamilies.match_attention(full, False).source  # (not causal: every item is as long as the next)
     odd = load(tmp_path, problems.attention(batch=1, heads=1, seq=128, dim=32, ident="d32"), "k_attention")
     with pytest.raises(families.Refusal, match="head dimension"):
         tcfamilies.match_attention(odd, False)
@@ -120,6 +127,12 @@ def test_mlp_is_taken_with_its_chain_and_refused(tmp_path):
     assert [bool(p.get("pdl")) for p in plan.pre] == [False, False, True] and "griddepcontrol.launch_dependents" in plan.source
     scratch = {p["name"]: p["bytes"] for pre in plan.pre for p in pre["params"] if p["kind"] == "scratch"}
     assert scratch == {"w1t": 512 * 256 * 2, "w2t": 256 * 512 * 2, "h": 128 * 512 * 2}
+    # the decode that runs alone streams 64 x 128 tiles; the one that runs beside the first matmul keeps 64 x 64 tiles
+    assert plan.pre[0]["grid"] == [(256 // 64) * (512 // 128), 1, 1] and "dequant_transpose_e4m3<false, true>" in plan.source
+    assert plan.pre[2]["grid"] == [(512 // 64) * (256 // 64), 1, 1] and "dequant_transpose_e4m3<true, false>" in plan.source
+    ragged = load(tmp_path, problems.gelu_mlp(tokens=128, d_model=160, hidden=320, lanes=8, block=64, ident="r"), "k_mlp_gelu")
+    plan_r = tcfamilies.match_mlp(ragged, False)
+    assert plan_r.pre[0]["grid"] == [3 * 5, 1, 1] and "dequant_transpose_e4m3<false, false>" in plan_r.source
     with pytest.raises(families.Refusal, match="own order"):
         tcfamilies.match_mlp(src, True)
     # a different activation constant is not the tanh-form GELU
