@@ -103,3 +103,29 @@ def test_mlp_full_size_sampled_cells_and_cross_check():
     w2 = prob.tensors["w2"].view(torch.float8_e4m3fn).float() * prob.tensors["w2_scale"]
     ref = (torch.nn.functional.gelu(x @ w1, approximate="tanh") @ w2).cpu().numpy()
     check(got, ref)
+
+
+@pytest.mark.parametrize("d_model,hidden", [(256, 256), (200, 264)])
+def test_weight_decode_of_every_code(tmp_path, d_model, hidden):
+    """The MLP's weight decode kernels (e4m3 codes [k][n] -> bf16 [n][k]) on weights that hold every one of the 256 codes:
+    the streaming 64 x 128 path (w1, shapes that divide), the 64 x 64 path beside the first matmul (w2) and on ragged
+    shapes. Every e4m3 value is a bf16 value, so the decoded scratch buffers are compared bit for bit with the definition
+    (ml_dtypes, as tests/test_fp8.py), NaN codes as NaN."""
+    import ml_dtypes
+    import torch
+    p = problems.gelu_mlp(tokens=128, d_model=d_model, hidden=hidden, lanes=8, block=64, ident="t")
+    folder = problems.write(p, tmp_path)
+    host = dict(runner.Problem(folder, "optimized").host)
+    rng = np.random.default_rng(1)
+    for name in ("w1", "w2"):
+        codes = np.resize(rng.permutation(np.repeat(np.arange(256, dtype=np.uint8), 4)), host[name].size)
+        host[name] = codes.reshape(host[name].shape)
+    prob = runner.Problem(folder, "optimized", inputs=host)
+    prob.run()
+    scratch = {k.split(".")[-1]: v for k, v in prob.tensors.items() if "." in k}
+    for name, key in (("w1", "w1t"), ("w2", "w2t")):
+        want = host[name].view(ml_dtypes.float8_e4m3fn).astype(np.float32).T
+        got = scratch[key].view(torch.bfloat16).reshape(want.shape).float().cpu().numpy()
+        nan = np.isnan(want)
+        assert nan.sum() >= 8 and np.array_equal(np.isnan(got), nan)
+        assert np.array_equal(got[~nan].view(np.uint32), want[~nan].view(np.uint32))  # (signed zeros included)
