@@ -50,6 +50,8 @@ ATTN_POLY_PERIOD_64 = 0
 # row each, maxima exchanged through shared memory). Measured SLOWER (1090 against 998 us): the exchange costs more than the
 # shorter per-tile chain saves, so 2 is only taken when EMMY_PTX_PREFER=split2 asks for it.
 ATTN_ROW_SPLIT = 1
+GEMM_PAIR_GROUP_M_H = 16  # 256-row tiles per group of a chain matmul with a short contraction (K <= 4096), as GEMM_GROUP_M_H
+MLP_GEMM_PAIRS = True  # the MLP chain's matmuls on CTA pairs where the matmul template would take them
 # K and V of all heads up to this size: work items longest first over all heads instead of head by head. Measured on causal
 # 4096 x 128 f16, one B200: 32 heads (64 MiB) 147.7 -> 129.4 us, 64 heads (128 MiB) 264.1 -> 261.8 us, 128 heads 503.9 -> 543.6 us.
 ATTN_L2_RESIDENT_BYTES = 128 << 20
@@ -643,10 +645,23 @@ def match_mlp(src, strict: bool, disable=frozenset()) -> Plan:
         return Plan("clusters", "\n".join(lines) + "\n", remarks, grid=clusters * C, block=256, cluster=C, smem_bytes=smem,
                     extra_params=extra, pre=pre)
 
-    stage = (128 + 256) * 64 * 2
-    smem = GEMM_STAGES * stage + 1024 + 256
-    tiles1 = math.ceil(T / 128) * math.ceil(Hd / 256)
-    tiles2 = math.ceil(T / 128) * math.ceil(D / 256)
+    # each matmul of the chain on the geometry the matmul template would take for its shape: CTA pairs (cta_group::2,
+    # 256 x 256 tiles) when there are enough tiles for every pair of SMs, else lone CTAs
+    def chain_gemm(M, N, K, lone_group, epi):
+        g = gemm_geometry(M, N) if MLP_GEMM_PAIRS else dict(gemm_geometry(M, N), kernel="")
+        if g["kernel"] != "gemm_tn_pair_kernel":
+            tiles = math.ceil(M / 128) * math.ceil(N / 256)
+            stage = (128 + 256) * 128
+            g = dict(kernel="gemm_tn_kernel", stages=GEMM_STAGES, group=lone_group, b_rows=256, tiles=tiles, tile="128 x 256",
+                     grid=min(TARGET_SMS, tiles), cluster=1, smem=GEMM_STAGES * stage + 1024 + 256)
+        if g["cluster"] == 2 and K <= 4096:
+            g["group"] = GEMM_PAIR_GROUP_M_H
+        g["call"] = f"emb::{g['kernel']}<{g['stages']}, {g['group']}, true, emb::{epi}>"
+        g["attrs"] = "__cluster_dims__(2, 1, 1) " if g["cluster"] == 2 else ""
+        return g
+    g1 = chain_gemm(T, Hd, D, GEMM_GROUP_M_H, "EPI_SCALE_GELU")
+    g2 = chain_gemm(T, D, Hd, GEMM_GROUP_M, "EPI_SCALE")
+    tiles1, tiles2 = g1["tiles"], g2["tiles"]
     # launch order: decode w1, h = gelu(x w1), decode w2, y = h w2. The second decode does not need h: it is launched
     # programmatically dependent on the first matmul (which lets its dependents go at once), runs beside it on the SMs'
     # spare shared memory and threads, and one of its threads waits for the matmul at the very end, so the second matmul,
@@ -654,23 +669,22 @@ def match_mlp(src, strict: bool, disable=frozenset()) -> Plan:
     lines = ['#include "emb_gemm.cuh"', decode[0], *decode[1:4],
              f'extern "C" __global__ void __launch_bounds__(256) {e}__w2(const unsigned char* __restrict__ codes, __nv_bfloat16* __restrict__ out) {{',
              f"    emb::dequant_transpose_e4m3<true, false>(codes, out, {Hd}, {D});", "}",
-             f'extern "C" __global__ void __launch_bounds__(192, 1) {e}__h(const __grid_constant__ CUtensorMap tmap_x, '
+             f'extern "C" __global__ void {g1["attrs"]}__launch_bounds__(192, 1) {e}__h(const __grid_constant__ CUtensorMap tmap_x, '
              "const __grid_constant__ CUtensorMap tmap_w1t, __nv_bfloat16* __restrict__ h, const float* __restrict__ scale, "
              "unsigned* __restrict__ status) {",
              '    asm volatile("griddepcontrol.launch_dependents;");',
-             f"    emb::gemm_tn_kernel<{GEMM_STAGES}, {GEMM_GROUP_M_H}, true, emb::EPI_SCALE_GELU>(&tmap_x, &tmap_w1t, h, "
-             f"emb::GemmShape{{{T}, {Hd}, {D}}}, status, scale);", "}",
-             f'extern "C" __global__ void __launch_bounds__(192, 1) {e}({sig}, const __grid_constant__ CUtensorMap tmap_h, '
+             f"    {g1['call']}(&tmap_x, &tmap_w1t, h, emb::GemmShape{{{T}, {Hd}, {D}}}, status, scale);", "}",
+             f'extern "C" __global__ void {g2["attrs"]}__launch_bounds__(192, 1) {e}({sig}, const __grid_constant__ CUtensorMap tmap_h, '
              "const __grid_constant__ CUtensorMap tmap_w2t, unsigned* __restrict__ status) {",
-             f"    emb::gemm_tn_kernel<{GEMM_STAGES}, {GEMM_GROUP_M}, true, emb::EPI_SCALE>(&tmap_h, &tmap_w2t, p_{w.output}, "
-             f"emb::GemmShape{{{T}, {D}, {Hd}}}, status, p_{s2_buf});", "}"]
+             f"    {g2['call']}(&tmap_h, &tmap_w2t, p_{w.output}, emb::GemmShape{{{T}, {D}, {Hd}}}, status, p_{s2_buf});", "}"]
     w2_decode = dict(pre[1], pdl=True, grid=[decode_grid(Hd, D, False), 1, 1])  # (beside the matmul: the general path, see emb_dequant.cuh)
     pre = [pre[0],
-           dict(entry=f"{e}__h", grid=[min(TARGET_SMS, tiles1), 1, 1], block=[192, 1, 1], cluster=1, smem_bytes=smem,
-                params=[tmap("x", lx.input, "bf16", (D, T), (D * 2,), (64, 128)), tmap("w1t", "w1t", "bf16", (D, Hd), (D * 2,), (64, 256)),
+           dict(entry=f"{e}__h", grid=[g1["grid"], 1, 1], block=[192, 1, 1], cluster=g1["cluster"], smem_bytes=g1["smem"],
+                params=[tmap("x", lx.input, "bf16", (D, T), (D * 2,), (64, 128)),
+                        tmap("w1t", "w1t", "bf16", (D, Hd), (D * 2,), (64, g1["b_rows"])),
                         dict(kind="scratch", name="h", bytes=T * Hd * 2), dict(kind="buffer", name=s1_buf), dict(kind="status", name="status")]),
            w2_decode]
-    extra = [tmap("h", "h", "bf16", (Hd, T), (Hd * 2,), (64, 128)), tmap("w2t", "w2t", "bf16", (Hd, D), (Hd * 2,), (64, 256)),
+    extra = [tmap("h", "h", "bf16", (Hd, T), (Hd * 2,), (64, 128)), tmap("w2t", "w2t", "bf16", (Hd, D), (Hd * 2,), (64, g2["b_rows"])),
              dict(kind="status", name="status")]
     remarks = [f"MLP template: {T} tokens, d_model {D}, hidden {Hd}; the e4m3 weights are decoded once to bf16 (exactly) and "
                "transposed to K-major, then two tcgen05 matmuls: h = gelu_tanh(s1 x w1) with the activation in the first one's "
@@ -679,5 +693,5 @@ def match_mlp(src, strict: bool, disable=frozenset()) -> Plan:
                f"programmatically dependent on it, waits for it only at its end), {e} ({tiles2} tiles); "
                f"scratch: {(2 * Hd * D * 2 + T * Hd * 2) >> 20} MiB",
                f"not fused in a cluster: {fused_why}; h makes one bf16 round trip through L2 / HBM between the two matmuls"]
-    return Plan("clusters", "\n".join(lines) + "\n", remarks, grid=min(TARGET_SMS, tiles2), block=192, smem_bytes=smem,
+    return Plan("clusters", "\n".join(lines) + "\n", remarks, grid=g2["grid"], block=192, cluster=g2["cluster"], smem_bytes=g2["smem"],
                 extra_params=extra, pre=pre)
