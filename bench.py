@@ -109,7 +109,7 @@ CHUNKED = ("mlp", "matmul", "attention", "fragments")  # e2e in slices of the un
 DEFAULT_FAMILIES = "sum,softmax,matmul,attention,elementwise,elementwise_add,sum_scalar,fragments,mlp_2048,mlp_2048_fused"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel at the one-GPU size, from the ncu
 # captures summarised under profiles/ (None until captured)
-NCU_TRAFFIC = {"softmax": 212.3e6, "sum": 67.5e6, "matmul": 1253.1e6, "attention": 1057.0e6, "mlp": 1204.9e6, "fragments": 1326.0e6,
+NCU_TRAFFIC = {"softmax": 212.3e6, "sum": 67.5e6, "matmul": 1253.1e6, "attention": 1057.0e6, "mlp": 1380.1e6, "fragments": 1326.0e6,
                "elementwise": 219.5e6, "elementwise_add": 359.3e6, "sum_scalar": 67.5e6, "mlp_2048_fused": 775.1e6}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
