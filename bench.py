@@ -549,9 +549,10 @@ def main() -> None:
         pipelined = prob.rows_pipeline(chunks=8, streams=4)
         chunked = None
         if pipelined is None and pl is not None and workload in CHUNKED and exchange is None:
-            # several launches, tensor maps: the same overlap by compiling the rank's share in four slices of its units
+            # several launches, tensor maps: the same overlap by compiling the rank's share in slices of its units
             try:
-                chunked = pipeline.ChunkedProblem(workload, kw, prob.host, args.mode, local, chunks=4, streams=3, root=scratch_root)
+                chunked = pipeline.ChunkedProblem(workload, kw, prob.host, args.mode, local, chunks=pipeline.slice_count(len(pl["share"])),
+                                                  streams=4, root=scratch_root)
             except Exception as e:  # noqa: BLE001 - the plain sequence below still measures the call
                 chunked = None
                 timing["chunked_e2e_unavailable"] = f"{type(e).__name__}: {e}"[:200]
@@ -577,7 +578,7 @@ def main() -> None:
         e2e = dict(value=all_max(statistics.mean(times)), unit="us", h2d_bytes_per_step=int(all_sum(h2d)), d2h_bytes_per_step=int(all_sum(d2h)),
                    resident=resident,
                    how=("8 row slices on 4 streams: copy in, launch, copy out overlap" if pipelined is not None else
-                        "4 slices of the units, each compiled for its size, on 3 streams: copy in, launches, copy out overlap; "
+                        f"{len(chunked.parts)} slices of the units, each compiled for its size, on 4 streams: copy in, launches, copy out overlap; "
                         "preparation of resident operands (weight decode) once per step" if chunked is not None else
                         "copy in, launches, copy out on one stream") + "; bytes are the sum over ranks")
         if chunked is not None:
