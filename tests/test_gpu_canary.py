@@ -72,3 +72,27 @@ def test_a_problem_run_in_slices_gives_the_whole_problems_output(tmp_path, workl
         chunked.check_status()
         got = runner.to_numpy(host_out[out_name], prob.dtypes[out_name])
         assert np.array_equal(got.view(np.uint16), whole.view(np.uint16))
+
+
+def test_the_full_size_mlp_in_the_benchs_slices_gives_the_whole_problems_output():
+    """The headline workload the way bench.py's end-to-end leg runs it: pipeline.slice_count slices (eight) on four streams,
+    matmuls on CTA pairs, the weight decode once per call; the bits are the whole problem's."""
+    import torch
+    from pathlib import Path
+    from emmy_ptx import multi, pipeline
+    folder = Path(runner.__file__).resolve().parent.parent / "problems" / "k_mlp_gelu_tanh_16384x4096x16384"
+    prob = runner.Problem(folder, "optimized")
+    whole = prob.run()["mlp"]
+    units = multi.plan("mlp", 0, 1)["units"]
+    chunked = pipeline.ChunkedProblem("mlp", dict(multi.FULL_SIZES["mlp"]), prob.host, "optimized", 0,
+                                      chunks=pipeline.slice_count(units), streams=4)
+    assert len(chunked.parts) == 8 and len(chunked.prepare) == 2
+    pinned = {n: prob.tensors[n].cpu().pin_memory() for n in chunked.plans[0]["slices"]}
+    host_out = {"mlp": torch.zeros(prob.tensors["mlp"].shape, dtype=prob.tensors["mlp"].dtype).pin_memory()}
+    for _ in range(2):
+        host_out["mlp"].zero_()
+        chunked.run(pinned, host_out)
+        torch.cuda.synchronize()
+        chunked.check_status()
+        got = runner.to_numpy(host_out["mlp"], prob.dtypes["mlp"])
+        assert np.array_equal(got.view(np.uint16), whole.view(np.uint16))
