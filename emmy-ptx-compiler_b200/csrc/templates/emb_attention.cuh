@@ -293,7 +293,9 @@ __device__ __forceinline__ void attention_fwd_kernel(const CUtensorMap* __restri
             const int n_mine = item.n_kv[i < NQ ? i : 0];
             const int q_row = item.q0 + i * BM + row;
             const int row_base = item.row_base;
-            float m_used = -__int_as_float(0x7f800000);  // -inf, in units of log2
+            // the reference maximum, in units of log2, seeded like the interpreter's maximum fold (-1e30, finite): a first key
+            // tile whose scores are all -inf (an additive mask) then gives weights 2^(-inf + 1e30) = 0, not NaN
+            float m_used = -1e30f;
             float l = 0.0f;
             float carried_max = -__int_as_float(0x7f800000);  // the previous tile's row maximum (raw score), not yet in m_used
             for (int j = 0; alive && j < n_mine; ++j, ++steps) {

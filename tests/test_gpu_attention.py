@@ -264,3 +264,34 @@ def test_attention_in_its_other_forms(tmp_path, monkeypatch, form, marker, seq, 
         prob.check_canaries()
         check(got.reshape(-1, dim)[blocks], rows[blocks], dtype, f"{form} S={seq} D={dim} sampled rows vs oracle")
         check(got, want, dtype, f"{form} S={seq} D={dim} all rows vs f64")
+
+
+@pytest.mark.parametrize("form", ["", "keys128"])
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_with_minus_infinity_in_the_mask(tmp_path, monkeypatch, form, causal):
+    """The reference's masked-keys test of its blocked softmax (tests/test_blocking.py:191-212: -inf scores leave the fold
+    exact, even for a whole block) on the template: scattered keys and whole key tiles at -inf - without the causal limit
+    the FIRST tile, so the running maximum is still at its seed when the first finite score arrives."""
+    monkeypatch.setenv("EMMY_PTX_PREFER", form)
+    seq = 320
+    p = problems.attention(batch=1, heads=2, seq=seq, dim=128, causal=causal, mask=True, ident="t")
+    folder = problems.write(p, tmp_path)
+    rng = np.random.default_rng(5)
+    host = {n: rng.standard_normal((1, 2, seq, 128)).astype(np.float16) for n in "qkv"}
+    mask = np.where(rng.random(seq) < 0.3, -np.inf, 0.0).astype(np.float32)
+    if causal:
+        mask[128:256] = -np.inf
+        mask[0] = 0.0  # (the first query sees key 0 only)
+    else:
+        mask[0:128] = -np.inf
+        mask[300] = 0.0
+    host["mask"] = mask
+    prob = runner.Problem(folder, "optimized", inputs=host, canary=True)
+    assert prob.kernels[0].launch_info["family"] == "blocking"
+    got = prob.run()["attn"]
+    prob.check_canaries()
+    assert np.isfinite(got.astype(np.float32)).all()
+    blocks = ragged_rows(2, seq)
+    want = oracle_problem(p, host, blocks=blocks)["attn"].reshape(-1, 128)
+    check(got.reshape(-1, 128)[blocks], want[blocks], "f16", f"-inf mask S={seq} causal={causal} {form} sampled rows vs oracle")
+    check(got, f64_attention(host, causal, float(np.float32(1 / np.sqrt(128))), mask), "f16", f"-inf mask S={seq} causal={causal} {form} all rows vs f64")
