@@ -208,7 +208,7 @@ def oracle_sample(workload: str, budget_s: float, workers: int, host: dict | Non
     if WORKLOADS[workload].get("oracle") == "fragment":  # the interpreter's extension to the tensor-core statements
         from oracle import fragment_oracle as ir_oracle
     p, meta_args = full_problem(workload)
-    total_us, notes = 0.0, []
+    total_us, notes, cores = 0.0, [], 1
     scale, reduced = 1.0, ""
     if host is None:  # the interpreter indexes the real buffers: generate the real inputs once
         host = {}
@@ -250,9 +250,10 @@ def oracle_sample(workload: str, budget_s: float, workers: int, host: dict | Non
             spent += time.perf_counter() - t0
             done += len(blocks)
         total_us += spent / done * grid * 1e6 * scale
+        cores = max(cores, used)
         notes.append(f"{kern['entry']}: {reduced}{done} of {grid} CTAs (seeded random choice) interpreted in {spent:.1f} s on up to {used} "
                      "core(s), scaled to the grid")
-    return dict(value=total_us, unit="us", cores=max(1, workers), kind="port", sample="; ".join(notes) +
+    return dict(value=total_us, unit="us", cores=cores, kind="port", sample="; ".join(notes) +
                 " (oracle/ir_oracle.py: numpy restatement of the reference's interpreter; extrapolated)")
 
 
